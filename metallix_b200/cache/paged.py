@@ -90,7 +90,7 @@ class PagedCache:
                 raise ValueError(f"unknown cache need {need.kind!r}")
         host = build.host()
         self.manager = host.CacheManager(
-            [host.GroupConfig(page_tokens, g.need.window or 0, g.num_pages) for g in self.groups],
+            [host.GroupConfig(page_tokens, g.need.window or 0, g.num_pages, g.need.chunk or 0) for g in self.groups],
             max_requests)
         if allocate:
             for group in self.groups:

@@ -15,6 +15,7 @@ import os
 from dataclasses import dataclass
 from typing import Any, Dict, Mapping, Optional, Type
 
+from .mekazen import MekazenConfig
 from .qwen3 import ConfigError, Qwen3Config
 
 
@@ -61,10 +62,13 @@ def family_by_kind(kind: str) -> ModelFamily:
 
 
 def resolve(raw: Mapping[str, Any]) -> ModelFamily:
-    """The family a ``config.json`` names, by ``architectures[0]`` or ``model_type``."""
+    """The family a ``config.json`` names, by ``architectures[0]``, a single
+    ``architecture`` or ``model_type``."""
     architectures = raw.get("architectures") or []
     if not isinstance(architectures, list):
         raise ConfigError("Json", "architectures must be a list of names")
+    if isinstance(raw.get("architecture"), str):
+        architectures = architectures + [raw["architecture"]]
     for name in architectures:
         if name in _BY_ARCHITECTURE:
             return _BY_ARCHITECTURE[name]
@@ -121,3 +125,6 @@ def _generation_eos(path: str) -> tuple:
 QWEN3 = ModelFamily(architecture=Qwen3Config.ARCHITECTURE, model_type=Qwen3Config.MODEL_TYPE,
                     kind="qwen", config_class=Qwen3Config)
 register(QWEN3)
+MEKAZEN = ModelFamily(architecture=MekazenConfig.ARCHITECTURE, model_type=MekazenConfig.MODEL_TYPE,
+                      kind="mekazen", config_class=MekazenConfig)
+register(MEKAZEN)

@@ -44,9 +44,13 @@ class LayerSpec:
     name: str  # tensor-name prefix, e.g. "model.layers.3"
     block: PartSpec  # the arrangement (pre-norm residual, ...)
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]        # None: the layer has no feed-forward
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
+    # Norms a sublayer's output passes before it joins the residual stream
+    # (an arrangement that has none ignores them).
+    mixer_post_norm: Optional[PartSpec] = None
+    feed_forward_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -74,7 +78,9 @@ class CacheNeed:
 
     ``kind == "kv_pages"``: keys and values of ``kv_heads`` heads of width
     ``head_dim`` for every position (``window is None``) or for the last
-    ``window`` positions. ``kind == "state"``: ``state_shape`` values of fixed
+    ``window`` positions; with ``chunk`` only the positions of the chunk of
+    that many positions (counted from position 0) the next query lies in are
+    ever read again. ``kind == "state"``: ``state_shape`` values of fixed
     size per request, zeroed when the request is admitted. ``kind == "none"``:
     the mixer keeps nothing between steps.
     """
@@ -83,11 +89,12 @@ class CacheNeed:
     kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None
+    chunk: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
 
     def group_key(self) -> tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window,
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.chunk,
                 tuple(self.state_shape), self.state_dtype)
 
 

@@ -12,16 +12,18 @@ PYBIND11_MODULE(_mxb_host, m) {
   m.doc() = "metallix_b200 host runtime: paged cache accounting and continuous batching";
 
   py::class_<GroupConfig>(m, "GroupConfig")
-      .def(py::init([](int page_tokens, int window, int num_pages) {
+      .def(py::init([](int page_tokens, int window, int num_pages, int chunk) {
              GroupConfig g;
              g.page_tokens = page_tokens;
              g.window = window;
              g.num_pages = num_pages;
+             g.chunk = chunk;
              return g;
            }),
-           py::arg("page_tokens"), py::arg("window") = 0, py::arg("num_pages") = 0)
+           py::arg("page_tokens"), py::arg("window") = 0, py::arg("num_pages") = 0, py::arg("chunk") = 0)
       .def_readwrite("page_tokens", &GroupConfig::page_tokens)
       .def_readwrite("window", &GroupConfig::window)
+      .def_readwrite("chunk", &GroupConfig::chunk)
       .def_readwrite("num_pages", &GroupConfig::num_pages);
 
   static py::exception<OutOfPages> out_of_pages(m, "OutOfPages", PyExc_RuntimeError);

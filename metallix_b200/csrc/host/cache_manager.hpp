@@ -3,8 +3,10 @@
 // The reference's BlockManager (crates/core/engine/src/blocks/manager.rs:130-135)
 // keeps one uniform pool for all layers. Here layers with the same needs form a
 // group, and every group has pages and block tables of its own: a group either
-// keeps every position (window == 0) or only the last `window` positions, whose
-// older pages go back to the free list as soon as the window has passed them.
+// keeps every position (window == 0, chunk == 0), only the last `window`
+// positions, or only the positions of the chunk of `chunk` positions that the
+// next query lies in (chunks counted from position 0); pages that no later
+// query can see go back to the free list as soon as they have been passed.
 // The protocol per step is the reference's (crates/core/engine/src/blocks.rs:17-45):
 // reserve (all or nothing) -> the forward pass writes -> commit.
 // Beside the pages every request holds one slot of fixed-size state.
@@ -31,6 +33,7 @@ namespace mxb {
 struct GroupConfig {
   int page_tokens = 16;  // positions per page
   int window = 0;        // 0: every position is kept; else the last `window`
+  int chunk = 0;         // 0: no chunks; else queries see keys of their own chunk of this many positions only
   int num_pages = 0;     // pages of this group's pool
 };
 
@@ -52,6 +55,7 @@ class CacheManager {
     for (const GroupConfig& g : groups_) {
       if (g.page_tokens <= 0) throw std::invalid_argument("page_tokens must be positive");
       if (g.window < 0) throw std::invalid_argument("window must not be negative");
+      if (g.chunk < 0) throw std::invalid_argument("chunk must not be negative");
       if (g.num_pages < 0) throw std::invalid_argument("num_pages must not be negative");
     }
     free_pages_.resize(groups_.size());
@@ -142,7 +146,7 @@ class CacheManager {
   }
 
   // Marks `tokens` reserved positions as written, then gives back the pages of
-  // windowed groups that no later query can see.
+  // windowed or chunked groups that no later query can see.
   void commit(int64_t id, int64_t tokens) {
     Request& r = get(id);
     if (tokens < 0 || r.computed + tokens > r.reserved)
@@ -150,10 +154,13 @@ class CacheManager {
     r.computed += tokens;
     for (size_t g = 0; g < groups_.size(); ++g) {
       const GroupConfig& cfg = groups_[g];
-      if (cfg.window == 0) continue;
+      if (cfg.window == 0 && cfg.chunk == 0) continue;
       // The next query sits at position >= computed and sees keys
-      // > position - window, so keys below computed - window + 1 are dead.
-      int64_t first_needed = r.computed - cfg.window + 1;
+      // > position - window, so keys below computed - window + 1 are dead;
+      // it sees no key ahead of its own chunk, so keys below the start of the
+      // chunk that holds position `computed` are dead too.
+      int64_t first_needed = cfg.window > 0 ? r.computed - cfg.window + 1 : 0;
+      if (cfg.chunk > 0) first_needed = std::max<int64_t>(first_needed, r.computed - r.computed % cfg.chunk);
       if (first_needed <= 0) continue;
       int64_t dead_pages = first_needed / cfg.page_tokens;  // pages wholly below
       for (int64_t p = r.first_live[g]; p < dead_pages && p < static_cast<int64_t>(r.tables[g].size()); ++p) {

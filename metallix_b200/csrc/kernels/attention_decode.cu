@@ -60,7 +60,7 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
                               int max_pages, const int* __restrict__ row_token,
                               const int* __restrict__ row_request, const int* __restrict__ positions,
                               int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                              int window, float scale, int* status) {
+                              int window, int chunk, float scale, int* status) {
   constexpr int E = Vec16<T>::kElems;  // elements per 16-byte piece
   constexpr int LPK = HD / E;          // 16-byte pieces (and lanes) per key row
   constexpr int KPW = 32 / LPK;        // key rows a warp reads at once
@@ -81,7 +81,7 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
   if (token < 0) return;  // a padding row
   const int pos = positions[token];
   const int group = heads / kv_heads;  // query heads per key/value head, <= G
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window, chunk);
   const int begin = max(split * kSplitKeys, first_key);
   const int end = min((split + 1) * kSplitKeys, pos + 1);
   if (begin >= end) return;  // the merge skips splits outside [first_key, pos]
@@ -253,7 +253,7 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
                                   int max_pages, const int* __restrict__ row_token,
                                   const int* __restrict__ row_request, const int* __restrict__ positions,
                                   int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                                  int window, float scale, int* status) {
+                                  int window, int chunk, float scale, int* status) {
   constexpr int ROW_BYTES = HD * 2;
   constexpr int TILE_BYTES = kSplitKeys * (ROW_BYTES + 16);
   extern __shared__ __align__(128) unsigned char mma_shared[];
@@ -271,7 +271,7 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
   if (token < 0) return;
   const int pos = positions[token];
   const int group = heads / kv_heads;  // <= 8
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window, chunk);
   const int begin = max(split * kSplitKeys, first_key);
   const int end = min((split + 1) * kSplitKeys, pos + 1);
   if (begin >= end) return;
@@ -467,7 +467,7 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
                                   int max_pages, const int* __restrict__ row_token,
                                   const int* __restrict__ row_request, const int* __restrict__ positions,
                                   int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                                  int window, float scale, int* status) {
+                                  int window, int chunk, float scale, int* status) {
   constexpr int HALVES = HD / kTmaColumns;                 // 64-value halves of a row
   constexpr int TILE_BYTES = kSplitKeys * HD * 2;
   extern __shared__ unsigned char tma_decode_raw[];
@@ -507,7 +507,7 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
   if (token < 0) return;
   const int pos = positions[token];
   const int group = heads / kv_heads;  // <= 8
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window, chunk);
   if (key0 > pos || key0 + kSplitKeys <= first_key) return;   // the merge skips splits outside [first_key, pos]
   const int lo = max(first_key - key0, 0), hi = min(pos - key0, kSplitKeys - 1);   // the split's rows that count
 
@@ -687,7 +687,7 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
                                        int max_pages, const int* __restrict__ row_token,
                                        const int* __restrict__ row_request, const int* __restrict__ positions,
                                        int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                                       int window, float scale, int* status) {
+                                       int window, int chunk, float scale, int* status) {
   constexpr int HALVES = HD / kTmaColumns;                 // 64-value halves of a row
   constexpr int TILE_BYTES = kSplitKeys * HD * 2;
   extern __shared__ unsigned char tma_decode_raw[];
@@ -712,13 +712,13 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
   const int table_row = row_request[row];
   const int* table = block_tables + static_cast<size_t>(table_row) * max_pages;
   // The page of this block's first tile is asked for together with the
-  // position, on the guess that no window has moved the first tile.
+  // position, on the guess that neither a window nor a chunk has moved the first tile.
   int page = 0;
   if (fetcher && rank * pages + slot < max_pages) page = table[rank * pages + slot];
   if (token < 0) return;   // a padding row
   const int pos = positions[token];
   const int group = heads / kv_heads;  // <= 8
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window, chunk);
   const int first_tile = first_key / kSplitKeys, last_tile = pos / kSplitKeys;
   int tile = first_tile + rank;
   if (first_tile > 0) {
@@ -930,14 +930,14 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
-                             int rows, int heads, int head_dim, int max_splits, int window, int slots,
+                             int rows, int heads, int head_dim, int max_splits, int window, int chunk, int slots,
                              int* status) {
   chain_release();
   const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
   if (token < 0 || d >= head_dim) return;
   const int pos = positions[token];
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window, chunk);
   const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
   if (last_split >= max_splits) {
     // The caller's bound on the contexts does not cover this row: its partial
@@ -999,7 +999,7 @@ template <typename T, int HD, int G>
 static int launch_decode(const void* q, const void* cache, void* out, float* partial,
                          const int* block_tables, int max_pages, const int* row_token,
                          const int* row_request, const int* positions, int rows, int heads,
-                         int kv_heads, int page_tokens, int num_pages, int max_splits, int window,
+                         int kv_heads, int page_tokens, int num_pages, int max_splits, int window, int chunk,
                          float scale, int* status, cudaStream_t stream) {
   dim3 grid(max_splits, kv_heads, rows);
   constexpr int kElems = Vec16<T>::kElems;
@@ -1014,13 +1014,13 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   }
   kernel<<<grid, kDecodeThreads, shared, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(cache), partial, block_tables, max_pages,
-      row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits, window,
+      row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk,
       scale, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
-                                         row_token, positions, rows, heads, HD, max_splits, window, 0, status));
+                                         row_token, positions, rows, heads, HD, max_splits, window, chunk, 0, status));
 }
 
 static int decode_resident_blocks = 444;   // blocks of the decode attention that fit the GPU at once (3 an SM); 0: always one block per tile
@@ -1030,19 +1030,19 @@ template <int HD>
 static int launch_decode_mma(const void* q, const void* cache, void* out, float* partial,
                              const int* block_tables, int max_pages, const int* row_token,
                              const int* row_request, const int* positions, int rows, int heads,
-                             int kv_heads, int page_tokens, int num_pages, int max_splits, int window,
+                             int kv_heads, int page_tokens, int num_pages, int max_splits, int window, int chunk,
                              float scale, int* status, cudaStream_t stream, DecodeProject project = DecodeProject()) {
   static_assert(kSplitKeys == kDecodeThreads, "one thread per key row of a split");
   auto finish = [&](int slots) -> int {
     if (project.w != nullptr)
       return static_cast<int>(launch_merge_project<HD>(partial, project.w, project.ldw, project.summands, row_token,
                                                        positions, rows, project.tokens, heads, project.hidden,
-                                                       max_splits, window, slots, kSplitKeys, kDecodeMinusHuge, status,
+                                                       max_splits, window, chunk, slots, kSplitKeys, kDecodeMinusHuge, status,
                                                        stream));
     return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                            dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
                                            static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
-                                           row_token, positions, rows, heads, HD, max_splits, window, slots, status));
+                                           row_token, positions, rows, heads, HD, max_splits, window, chunk, slots, status));
   };
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
@@ -1074,7 +1074,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
       if (attribute != cudaSuccess) return static_cast<int>(attribute);
       e = launch_chained(kernel, dim3(slots, kv_heads, rows), dim3(kDecodeThreads), shared, stream, map_cache,
                          static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
-                         positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+                         positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status);
       if (e != cudaSuccess) return static_cast<int>(e);
       return finish(slots);
     }
@@ -1083,7 +1083,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
     if (attribute != cudaSuccess) return static_cast<int>(attribute);
     e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream, map_cache,
                        static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
-                       positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+                       positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status);
   } else {
     const int shared = 2 * kSplitKeys * (HD * 2 + 16);
     auto kernel = paged_attention_decode_mma_kernel<HD>;
@@ -1092,7 +1092,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
     e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream,
                        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
                        partial, block_tables, max_pages, row_token, row_request, positions, heads,
-                       kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+                       kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status);
   }
   if (e != cudaSuccess) return static_cast<int>(e);
   return finish(0);
@@ -1131,14 +1131,14 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
                                        const int* block_tables, int max_pages, const int* row_token,
                                        const int* row_request, const int* positions, int rows,
                                        int heads, int kv_heads, int head_dim, int page_tokens,
-                                       int num_pages, int max_splits, int window, float scale,
+                                       int num_pages, int max_splits, int window, int chunk, float scale,
                                        int dtype, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) || max_splits <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const int group = heads / kv_heads;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
-             heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status, stream
+             heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream
 #define BY_GROUP(T, HD)                                        \
   if (group == 1) return launch_decode<T, HD, 1>(ARGS);        \
   if (group == 2) return launch_decode<T, HD, 2>(ARGS);        \
@@ -1173,7 +1173,7 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
                                                const int* block_tables, int max_pages, const int* row_token,
                                                const int* row_request, const int* positions, int rows, int tokens,
                                                int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
-                                               int max_splits, int window, float scale, const void* w, long long ldw,
+                                               int max_splits, int window, int chunk, float scale, const void* w, long long ldw,
                                                int hidden, float* summands, int* status, cudaStream_t stream) {
   if (rows <= 0 || hidden <= 0 || max_splits <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_paged_attention_decode_project_supported(head_dim, heads, kv_heads, kBF16, tokens, w, ldw))
@@ -1186,7 +1186,7 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
   project.summands = summands;
   void* out = nullptr;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
-             heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status, stream, project
+             heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
   return head_dim == 64 ? launch_decode_mma<64>(ARGS) : launch_decode_mma<128>(ARGS);
 #undef ARGS
 }
@@ -1255,7 +1255,7 @@ MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache,
   if (e != cudaSuccess) return static_cast<int>(e);
   return mxb_paged_attention_decode(q, cache, out, scratch, block_tables, max_pages, row_token,
                                     row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
-                                    num_pages, splits, window, scale, dtype, status, stream);
+                                    num_pages, splits, window, 0, scale, dtype, status, stream);
 }
 
 MXB_TIMELINE_EXPORT(mxb_timeline_attention)

@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kProjectThreads)
 decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ w, long long ldw,
                             float* __restrict__ summands, const int* __restrict__ row_token,
                             const int* __restrict__ positions, int rows, int tokens, int heads, int hidden,
-                            int max_splits, int window, int slots, int split_keys, float minus_huge, int* status) {
+                            int max_splits, int window, int chunk, int slots, int split_keys, float minus_huge, int* status) {
   constexpr int PITCH = HD * 2 + 16;  // bytes per row of a tile: rows a warp reads together fall on all banks
   constexpr int X_ROWS = MB * 8;
   extern __shared__ __align__(128) unsigned char project_shared[];
@@ -74,7 +74,7 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
     const int token = row_token[row];
     if (token < 0 || token >= X_ROWS) continue;
     const int pos = positions[token];
-    const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first_key = first_visible_key(pos, window, chunk);
     const int first_split = first_key / split_keys, last_split = pos / split_keys;
     if (last_split >= max_splits) {
       if (lane == 0) atomicOr(status, kStatusBadSlot);
@@ -215,7 +215,7 @@ static bool decode_project_takes(int head_dim, int tokens, const void* w, long l
 template <int HD>
 static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat16* w, long long ldw, float* summands,
                                         const int* row_token, const int* positions, int rows, int tokens, int heads,
-                                        int hidden, int max_splits, int window, int slots, int split_keys,
+                                        int hidden, int max_splits, int window, int chunk, int slots, int split_keys,
                                         float minus_huge, int* status, cudaStream_t stream) {
   const dim3 grid((hidden + kProjectColumns - 1) / kProjectColumns, heads);
 #define GO(MB)                                                                                                       \
@@ -227,7 +227,7 @@ static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat1
       if (e != cudaSuccess) return e;                                                                                \
     }                                                                                                                \
     return launch_chained(kernel, grid, dim3(kProjectThreads), shared, stream, partial, w, ldw, summands, row_token,  \
-                          positions, rows, tokens, heads, hidden, max_splits, window, slots, split_keys, minus_huge,  \
+                          positions, rows, tokens, heads, hidden, max_splits, window, chunk, slots, split_keys, minus_huge,  \
                           status);                                                                                   \
   }
   if (tokens <= 8) GO(1)

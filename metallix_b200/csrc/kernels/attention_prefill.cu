@@ -73,7 +73,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                      const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                      const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
-                     int kv_heads, int page_tokens, int num_pages, int window, float scale, int* status) {
+                     int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, int* status) {
   constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
   constexpr int TILE_BYTES = kFlashKeys * HD * 2;
   extern __shared__ __align__(128) unsigned char shared[];
@@ -90,7 +90,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   if (n <= 0) return;
   const int pos0 = positions[t0];
   const int last_pos = pos0 + n - 1;
-  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int first_key = first_visible_key(pos0, window, chunk);
   const int* table = block_tables + static_cast<size_t>(tile_request[tile]) * max_pages;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const size_t page_stride = static_cast<size_t>(2) * kv_heads * page_tokens * HD;
@@ -140,6 +140,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   const int g = lane >> 2, t = lane & 3;
   const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
   const int pos_lo = pos0 + row_lo, pos_hi = pos0 + row_hi;
+  const int first_lo = first_visible_key(pos_lo, window, chunk), first_hi = first_visible_key(pos_hi, window, chunk);
   const bool valid_lo = row_lo < n, valid_hi = row_hi < n;
   const float scale_log2 = scale * 1.4426950408889634f;
 
@@ -190,15 +191,15 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     // ---- mask, running maximum and sum (float32). m_* hold the running
     // maximum already multiplied by scale * log2(e).
     const int key0 = kt * kFlashKeys;
-    const bool all_seen = window <= 0 && n == kFlashQueries && key0 + kFlashKeys - 1 <= pos0;
+    const bool all_seen = window <= 0 && chunk <= 0 && n == kFlashQueries && key0 + kFlashKeys - 1 <= pos0;
     if (!all_seen) {
 #pragma unroll
       for (int nb = 0; nb < kFlashKeys / 8; ++nb) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int key = key0 + nb * 8 + 2 * t + j;
-          const bool seen_lo = valid_lo && key <= pos_lo && key >= first_key && (window <= 0 || key > pos_lo - window);
-          const bool seen_hi = valid_hi && key <= pos_hi && key >= first_key && (window <= 0 || key > pos_hi - window);
+          const bool seen_lo = valid_lo && key <= pos_lo && key >= first_lo;
+          const bool seen_hi = valid_hi && key <= pos_hi && key >= first_hi;
           if (!seen_lo) s[nb][j] = -INFINITY;
           if (!seen_hi) s[nb][2 + j] = -INFINITY;
         }
@@ -276,7 +277,7 @@ template <int HD>
 static int launch_flash(const void* q, const void* cache, void* out, const int* block_tables, int max_pages,
                         const int* tile_request, const int* tile_start, const int* tile_length,
                         const int* positions, int tiles, int heads, int kv_heads, int page_tokens,
-                        int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+                        int num_pages, int window, int chunk, float scale, int* status, cudaStream_t stream) {
   const int shared = 4 * kFlashKeys * HD * 2;
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
@@ -285,7 +286,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
   kernel<<<grid, kFlashThreads, shared, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,
-      positions, heads, kv_heads, page_tokens, num_pages, window, scale, status);
+      positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -306,13 +307,13 @@ MXB_API int mxb_flash_prefill_tile() { return 2 * kFlashQueries; }
 MXB_API int mxb_flash_prefill(const void* q, const void* cache, void* out, const int* block_tables,
                               int max_pages, const int* tile_request, const int* tile_start,
                               const int* tile_length, const int* positions, int tiles, int heads,
-                              int kv_heads, int head_dim, int page_tokens, int num_pages, int window,
+                              int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
                               float scale, int dtype, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (!mxb_flash_prefill_supported(head_dim, heads, kv_heads, dtype)) return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, scale, status, stream);
+                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, status, stream);
   return launch_flash<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, scale, status, stream);
+                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, status, stream);
 }

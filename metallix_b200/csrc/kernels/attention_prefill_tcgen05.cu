@@ -75,7 +75,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                              const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                              const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
-                             int kv_heads, int page_tokens, int num_pages, int window, float scale,
+                             int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale,
                              int shared_bytes, float* __restrict__ partial, int* status) {
   using Config = FaConfig<HD>;
   constexpr int MAX_STAGES = Config::kKeyStages;
@@ -118,7 +118,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   const int t0 = tile_start[tile], n = tile_length[tile];
   const int pos0 = positions[t0];
   const int last_pos = pos0 + n - 1;
-  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int first_key = first_visible_key(pos0, window, chunk);
   // The key tiles of this query tile. With gridDim.z > 1 they are shared out
   // among that many blocks (a portion of a prompt behind a long context is few
   // query tiles with many key tiles each: this way it still fills the GPU);
@@ -297,7 +297,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const bool valid = row < n;
     const int pos = pos0 + row;
     const int key_hi = valid ? pos : -1;                                   // last key this row sees
-    const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;          // first key this row sees
+    const int key_lo = first_visible_key(pos, window, chunk);          // first key this row sees
     const float scale_log2 = scale * 1.4426950408889634f;
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
     uint64_t* meet = &row_ready[warp & 3];
@@ -456,7 +456,7 @@ template <int HD>
 static int launch_flash_tc(const void* q, const void* cache, void* out, const int* block_tables, int max_pages,
                            const int* tile_request, const int* tile_start, const int* tile_length,
                            const int* positions, int tokens, int tiles, int heads, int kv_heads, int page_tokens,
-                           int num_pages, int window, float scale, int key_shares, float* partial, int* status,
+                           int num_pages, int window, int chunk, float scale, int key_shares, float* partial, int* status,
                            cudaStream_t stream) {
   using Config = FaConfig<HD>;
   CUtensorMap map_q, map_cache;
@@ -480,7 +480,7 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
   dim3 grid(heads, tiles, shared_out ? key_shares : 1);
   kernel<<<grid, kFaThreads, shared_bytes, stream>>>(
       map_q, map_cache, static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start,
-      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, scale, shared_bytes,
+      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, shared_bytes,
       shared_out ? partial : nullptr, status);
   e = cudaGetLastError();
   if (e != cudaSuccess || !shared_out) return static_cast<int>(e);
@@ -511,7 +511,7 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
                                       int max_pages, const int* tile_request, const int* tile_start,
                                       const int* tile_length, const int* positions, int tokens, int tiles,
                                       int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
-                                      int window, float scale, int dtype, int key_shares, float* partial,
+                                      int window, int chunk, float scale, int dtype, int key_shares, float* partial,
                                       int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (key_shares < 1 || key_shares > kMergeShares || (key_shares > 1 && partial == nullptr))
@@ -523,9 +523,9 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
     return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash_tc<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                               positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, scale,
+                               positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
                                key_shares, partial, status, stream);
   return launch_flash_tc<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                              positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, scale,
+                              positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
                               key_shares, partial, status, stream);
 }

@@ -12,7 +12,7 @@
 // Replaces the reference's gather of the whole context plus
 // fast::scaled_dot_product_attention (crates/models/qwen/src/forward/paged.rs:329-342,
 // :1067-1076, :1176-1184): s = (q k^T) * scale, causal with the diagonal at the
-// query's own position, optional window (key > position - window), softmax
+// query's own position, optional window (key > position - window) and chunk (key >= position - position % chunk), softmax
 // over keys, query head j reads key/value head j / (heads / kv_heads).
 #include "common.cuh"
 
@@ -30,7 +30,7 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
                             const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                             const int* __restrict__ tile_length, const int* __restrict__ positions,
                             int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
-                            int window, float scale, int* status) {
+                            int window, int chunk, float scale, int* status) {
   extern __shared__ float shared[];
   float* sQ = shared;                                   // [16][head_dim]
   float* sK = sQ + kTileQueries * head_dim;             // [32][head_dim + 1]
@@ -44,10 +44,11 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
   const int n = tile_length[tile];
   const int pos0 = positions[t0];
   const int last_pos = pos0 + n - 1;
-  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int first_key = first_visible_key(pos0, window, chunk);
   const int tid = threadIdx.x;
   const int r = tid >> 3, lane8 = tid & 7;
   const int my_pos = pos0 + r;
+  const int my_first = first_visible_key(my_pos, window, chunk);   // first key this row sees
   const bool row_valid = r < n;
   const int* table = block_tables + static_cast<size_t>(request) * max_pages;
 
@@ -95,7 +96,7 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
       const float* qrow = sQ + r * head_dim;
       const float* krow = sK + c * (head_dim + 1);
       for (int d = 0; d < head_dim; ++d) dot = fmaf(qrow[d], krow[d], dot);
-      visible[j] = row_valid && key <= my_pos && key >= first_key && (window <= 0 || key > my_pos - window);
+      visible[j] = row_valid && key <= my_pos && key >= my_first;
       s[j] = visible[j] ? dot * scale : kMinusHuge;
       tile_max = fmaxf(tile_max, s[j]);
     }
@@ -144,7 +145,7 @@ template <typename T, int DPT>
 static int launch_tile(const void* q, const void* cache, void* out, const int* block_tables,
                        int max_pages, const int* tile_request, const int* tile_start,
                        const int* tile_length, const int* positions, int tiles, int heads,
-                       int kv_heads, int head_dim, int page_tokens, int num_pages, int window,
+                       int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
                        float scale, int* status, cudaStream_t stream) {
   const size_t shared = sizeof(float) * (static_cast<size_t>(kTileQueries) * head_dim +
                                          static_cast<size_t>(kTileKeys) * (head_dim + 1) +
@@ -159,7 +160,7 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
   kernel<<<grid, kTileThreads, shared, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(cache), static_cast<T*>(out), block_tables,
       max_pages, tile_request, tile_start, tile_length, positions, heads, kv_heads, head_dim,
-      page_tokens, num_pages, window, scale, status);
+      page_tokens, num_pages, window, chunk, scale, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -175,12 +176,12 @@ MXB_API int mxb_paged_attention_tile(const void* q, const void* cache, void* out
                                      const int* tile_request, const int* tile_start,
                                      const int* tile_length, const int* positions, int tiles,
                                      int heads, int kv_heads, int head_dim, int page_tokens,
-                                     int num_pages, int window, float scale, int dtype, int* status,
+                                     int num_pages, int window, int chunk, float scale, int dtype, int* status,
                                      cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (head_dim <= 0 || head_dim > 256 || heads % kv_heads != 0) return static_cast<int>(cudaErrorInvalidValue);
 #define ARGS q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length, positions, \
-             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, scale, status, stream
+             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, status, stream
 #define DISPATCH(T)                                           \
   if (head_dim <= 16) return launch_tile<T, 2>(ARGS);         \
   if (head_dim <= 32) return launch_tile<T, 4>(ARGS);         \

@@ -61,6 +61,22 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// The first key a query at position `pos` sees. Two rules, either or both:
+// a sliding window keeps the last `window` positions (keys > pos - window), a
+// chunked mask keeps the keys of the query's own chunk of `chunk` positions,
+// counted from position 0 of the sequence (keys >= pos - pos % chunk). 0
+// turns a rule off. The result never decreases as `pos` grows, so the first
+// key of a tile of queries is that of its first row.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+  int first = window > 0 ? pos - window + 1 : 0;
+  if (first < 0) first = 0;
+  if (chunk > 0) {
+    const int chunk_start = pos - pos % chunk;
+    if (chunk_start > first) first = chunk_start;
+  }
+  return first;
+}
+
 // Programmatic dependent launch: a kernel launched through launch_chained()
 // may start while its predecessor in the stream is still running. It calls
 // chain_wait() before it touches anything the predecessor writes (the wait

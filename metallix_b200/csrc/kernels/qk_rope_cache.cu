@@ -6,6 +6,12 @@
 // scatter (crates/models/qwen/src/forward/paged.rs:300-325). Norm and rotation
 // run in float32; cos and sin come from a table built in float64.
 //
+// Two more forms, as parameters: the rotation may pair neighbouring values
+// (2i, 2i + 1) instead of halves (i, i + rotary_dim / 2), and the norm may run
+// over a token's whole projection (all query heads together, all key heads
+// together, weights of that width) instead of head by head; the second has a
+// kernel of its own below, one block per token.
+//
 // Cache layout of one layer: [pages, 2 (K, V), kv_heads, page_tokens, head_dim];
 // position p of a request lives in page table[p / page_tokens] at row
 // p % page_tokens, which the caller passes flattened as slot = page *
@@ -23,7 +29,7 @@ __global__ void qk_norm_rope_cache_kernel(
     const int* __restrict__ positions,
     const float* __restrict__ q_weight, const float* __restrict__ k_weight,  // null: no norm
     const float* __restrict__ cos_table, const float* __restrict__ sin_table,  // null: no rotation
-    int table_positions, int rotary_dim, int heads, int kv_heads, int head_dim, int page_tokens,
+    int table_positions, int rotary_dim, int interleaved, int heads, int kv_heads, int head_dim, int page_tokens,
     int num_pages, float eps, int* status) {
   extern __shared__ float head[];  // head_dim values
   __shared__ float scratch[33];
@@ -82,11 +88,14 @@ __global__ void qk_norm_rope_cache_kernel(
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float out = head[i];
     if (rotate && i < rotary_dim) {
-      const int j = i < half ? i : i - half;
+      // pair j is (j, j + half), or (2j, 2j + 1) when interleaved: the first of a
+      // pair becomes a cos - b sin, the second b cos + a sin
+      const bool first = interleaved ? (i & 1) == 0 : i < half;
+      const int j = interleaved ? i >> 1 : (first ? i : i - half);
+      const int partner = interleaved ? i ^ 1 : (first ? i + half : i - half);
       const float c = cos_table[static_cast<size_t>(pos) * half + j];
       const float s = sin_table[static_cast<size_t>(pos) * half + j];
-      // out[i] = x[i] cos - x[i + half] sin; out[i + half] = x[i + half] cos + x[i] sin
-      out = i < half ? head[i] * c - head[i + half] * s : head[i] * c + head[i - half] * s;
+      out = first ? head[i] * c - head[partner] * s : head[i] * c + head[partner] * s;
     }
     dst[i] = from_float<T>(out);
   }
@@ -243,6 +252,116 @@ qk_norm_rope_cache_warp_kernel(
   reinterpret_cast<Values*>(dst + HALF)[sub] = out_hi;
 }
 
+// The norm over a token's whole projection: one RMS over all query heads'
+// values (weights [heads * head_dim]) and one over all key heads', then the
+// rotation head by head, q to q_out, k and v into the cache. One block per
+// token; the two rows wait in shared memory as float32 between the sum of
+// squares and the rotation, whose partner may lie anywhere in the head. V
+// values of T move as one access where rows are aligned for it (V = 1: any
+// layout).
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+qk_rownorm_rope_cache_kernel(
+    const T* __restrict__ q_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
+    long long q_stride, long long k_stride, long long v_stride, T* __restrict__ q_out,
+    T* __restrict__ cache, const int* __restrict__ slots, const int* __restrict__ positions,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
+    int rotary_dim, int interleaved, int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
+    float eps, int* status) {
+  extern __shared__ float rows[];   // the q row, then the k row
+  __shared__ float scratch[33];
+  using Values = Pack<T, V>;
+  chain_release();
+  // Up to chain_wait(): the step's integers only.
+  const int t = blockIdx.x;
+  const int q_width = heads * head_dim, k_width = kv_heads * head_dim;
+  float* q_row = rows;
+  float* k_row = rows + q_width;
+  int pos = positions[t];
+  const bool rotate = cos_table != nullptr;
+  if (rotate && (pos < 0 || pos >= table_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+    pos = 0;
+  }
+  T* key_page = nullptr;   // row `row` of head 0 of the page's keys; values lie kv_heads heads further
+  if (slots != nullptr && cache != nullptr) {
+    const int slot = slots[t];
+    if (slot >= 0) {
+      const int page = slot / page_tokens, row = slot - page * page_tokens;
+      if (page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+      } else {
+        key_page = cache + (static_cast<size_t>(page) * 2 * kv_heads * page_tokens + row) * head_dim;
+      }
+    }
+  }
+  const size_t head_stride = static_cast<size_t>(page_tokens) * head_dim;   // from one head of a page to the next
+  chain_wait();
+  const T* q_src = behind_wait(q_in) + t * q_stride;   // written by the kernel ahead of this one
+  const T* k_src = behind_wait(k_in) + t * k_stride;
+  const T* v_src = behind_wait(v_in) + t * v_stride;
+
+  float q_sum = 0.0f, k_sum = 0.0f;
+  if (q_out != nullptr) {
+    for (int i = threadIdx.x * V; i < q_width; i += blockDim.x * V) {
+      const Values in = *reinterpret_cast<const Values*>(q_src + i);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float x = to_float(in.v[j]);
+        q_row[i + j] = x;
+        q_sum += x * x;
+      }
+    }
+  }
+  if (key_page != nullptr) {
+    for (int i = threadIdx.x * V; i < k_width; i += blockDim.x * V) {
+      const Values in = *reinterpret_cast<const Values*>(k_src + i);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float x = to_float(in.v[j]);
+        k_row[i + j] = x;
+        k_sum += x * x;
+      }
+      // values are stored as projected
+      const int kv = i / head_dim, d = i - kv * head_dim;
+      *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) =
+          *reinterpret_cast<const Values*>(v_src + i);
+    }
+  }
+  // block_sum's barriers also make the rows visible to every thread
+  q_sum = block_sum(q_sum, scratch);
+  k_sum = block_sum(k_sum, scratch);
+  const int half = rotary_dim >> 1;
+
+  auto finish = [&](const float* row, int width, float sum, const float* weight, bool is_q) {
+    const float scale = weight != nullptr ? rsqrtf(sum / static_cast<float>(width) + eps) : 1.0f;
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+      const int h = i / head_dim, d0 = i - h * head_dim;   // V divides head_dim: a vector stays in one head
+      Values out;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int d = d0 + j;
+        float x = row[i + j] * scale * (weight != nullptr ? weight[i + j] : 1.0f);
+        if (rotate && d < rotary_dim) {
+          const bool first = interleaved ? (d & 1) == 0 : d < half;
+          const int pair = interleaved ? d >> 1 : (first ? d : d - half);
+          const int partner = i + j + (interleaved ? (first ? 1 : -1) : (first ? half : -half));
+          const float y = row[partner] * scale * (weight != nullptr ? weight[partner] : 1.0f);
+          const float c = cos_table[static_cast<size_t>(pos) * half + pair];
+          const float s = sin_table[static_cast<size_t>(pos) * half + pair];
+          x = first ? x * c - y * s : x * c + y * s;
+        }
+        out.v[j] = from_float<T>(x);
+      }
+      if (is_q) *reinterpret_cast<Values*>(q_out + static_cast<size_t>(t) * width + i) = out;
+      else *reinterpret_cast<Values*>(key_page + h * head_stride + d0) = out;
+    }
+  };
+  if (q_out != nullptr) finish(q_row, q_width, q_sum, q_weight, true);
+  if (key_page != nullptr) finish(k_row, k_width, k_sum, k_weight, false);
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -251,19 +370,41 @@ MXB_API int mxb_qk_norm_rope_cache(
     const void* q_in, const void* k_in, const void* v_in, long long q_stride, long long k_stride,
     long long v_stride, void* q_out, void* cache, const int* slots, const int* positions,
     const float* q_weight, const float* k_weight, const float* cos_table, const float* sin_table,
-    int table_positions, int rotary_dim, int tokens, int heads, int kv_heads, int head_dim,
-    int page_tokens, int num_pages, float eps, int dtype, int* status, cudaStream_t stream) {
+    int table_positions, int rotary_dim, int interleaved, int norm_scope, int tokens, int heads, int kv_heads,
+    int head_dim, int page_tokens, int num_pages, float eps, int dtype, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return static_cast<int>(cudaErrorInvalidValue);
+  if (dtype != kF32 && dtype != kBF16) return static_cast<int>(cudaErrorInvalidValue);
   // The warp kernel moves 16 bytes per access: rows and bases must be aligned to that.
   const int element = dtype == kF32 ? 4 : 2;
   auto aligned = [&](const void* p, long long stride) {
     return p == nullptr || (reinterpret_cast<uintptr_t>(p) % 16 == 0 && (stride * element) % 16 == 0);
   };
+  if (norm_scope == 1) {
+    // One norm over the whole projection (weights [heads * head_dim] and
+    // [kv_heads * head_dim]): a block per token.
+    if (head_dim & 1) return static_cast<int>(cudaErrorInvalidValue);
+    const int vector = 16 / element;
+    const bool wide = head_dim % vector == 0 && aligned(q_in, q_stride) && aligned(k_in, k_stride) &&
+                      aligned(v_in, v_stride) && aligned(q_out, 0) && aligned(cache, 0);
+    const size_t shared = static_cast<size_t>(heads + kv_heads) * head_dim * sizeof(float);
+    cudaError_t launch_status = cudaSuccess;
+#define ROW_LAUNCH(T, V) do { \
+      auto kernel = qk_rownorm_rope_cache_kernel<T, V>; \
+      if (shared > 48 * 1024) launch_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
+      if (launch_status == cudaSuccess) launch_status = launch_chained(kernel, dim3(tokens), dim3(256), shared, stream, \
+        static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, v_stride, \
+        static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, sin_table, \
+        table_positions, rotary_dim, interleaved, heads, kv_heads, head_dim, page_tokens, num_pages, eps, status); } while (0)
+    if (dtype == kF32) { if (wide) ROW_LAUNCH(float, 4); else ROW_LAUNCH(float, 1); }
+    else { if (wide) ROW_LAUNCH(__nv_bfloat16, 8); else ROW_LAUNCH(__nv_bfloat16, 1); }
+#undef ROW_LAUNCH
+    return static_cast<int>(launch_status);
+  }
   const bool vector_ok = aligned(q_in, q_stride) && aligned(k_in, k_stride) && aligned(v_in, v_stride) &&
                          aligned(q_out, 0) && aligned(cache, 0) && aligned(q_weight, 0) && aligned(k_weight, 0) &&
                          aligned(cos_table, 0) && aligned(sin_table, 0);
-  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim) &&
+  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || (rotary_dim == head_dim && !interleaved)) &&
       vector_ok && (dtype == kF32 || dtype == kBF16)) {
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     if (items >= 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
@@ -290,14 +431,14 @@ MXB_API int mxb_qk_norm_rope_cache(
     qk_norm_rope_cache_kernel<float><<<grid, threads, shared, stream>>>(
         static_cast<const float*>(q_in), static_cast<const float*>(k_in), static_cast<const float*>(v_in),
         q_stride, k_stride, v_stride, static_cast<float*>(q_out), static_cast<float*>(cache), slots,
-        positions, q_weight, k_weight, cos_table, sin_table, table_positions, rotary_dim, heads,
+        positions, q_weight, k_weight, cos_table, sin_table, table_positions, rotary_dim, interleaved, heads,
         kv_heads, head_dim, page_tokens, num_pages, eps, status);
   else if (dtype == kBF16)
     qk_norm_rope_cache_kernel<__nv_bfloat16><<<grid, threads, shared, stream>>>(
         static_cast<const __nv_bfloat16*>(q_in), static_cast<const __nv_bfloat16*>(k_in),
         static_cast<const __nv_bfloat16*>(v_in), q_stride, k_stride, v_stride,
         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(cache), slots, positions,
-        q_weight, k_weight, cos_table, sin_table, table_positions, rotary_dim, heads, kv_heads,
+        q_weight, k_weight, cos_table, sin_table, table_positions, rotary_dim, interleaved, heads, kv_heads,
         head_dim, page_tokens, num_pages, eps, status);
   else
     return static_cast<int>(cudaErrorInvalidValue);

@@ -77,7 +77,7 @@ class DecodeGraphs:
         self.placements = PLACEMENTS
         self.placement_ms: Dict[Tuple[int, int], List[float]] = {}   # what each placement of a step took
         cache = engine.cache
-        self._windowed = any(g.need.window for g in cache.groups)
+        self._windowed = any(g.need.window or g.need.chunk for g in cache.groups)   # pages leave a table
         self.h2d_bytes = 0
         # Mirrors of the manager's tables: manager id -> (epoch, pages, per-group rows)
         self._host_tables: Dict[int, tuple] = {}

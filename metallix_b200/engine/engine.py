@@ -184,12 +184,14 @@ class Engine:
             self.release(request)
 
     # -------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], tap=None) -> Optional[torch.Tensor]:
         """Runs one batch. Returns float32 logits ``[wanted, vocab]`` on the
         device in the order of the entries and of each entry's ``want``, or
         None if nothing is wanted. The tensor may be a view of a buffer that
         the next step overwrites: read it before stepping again. Call
-        ``check()`` after reading results."""
+        ``check()`` after reading results. ``tap(index, residual)`` sees the
+        residual stream of the step's packed tokens after every layer run;
+        such a step is launched kernel by kernel."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(**e) for e in entries]
         ops.set_chained_launches(self.chained_launches)   # another engine may have chosen otherwise
         self._validate(entries)
@@ -205,7 +207,7 @@ class Engine:
                 if manager.computed(rid) == 0:
                     self.cache.zero_state(manager.slot(rid))  # a sequence starts from zero state
                 manager.reserve(rid, len(entry.tokens))
-            logits = self._run_graph(entries) if self._all_decode(entries) else self._run(entries)
+            logits = self._run_graph(entries) if tap is None and self._all_decode(entries) else self._run(entries, tap)
             for entry in entries:
                 manager.commit(self._rid(entry), len(entry.tokens))
         except BaseException:
@@ -248,11 +250,11 @@ class Engine:
         """Whether a decode step may be launched before the tokens it runs on
         have reached the host, to be confirmed or dropped afterwards: only
         when dropping leaves no trace, i.e. every cache entry is pages without
-        a window (a page written in vain is simply written again) and no part
+        a window or chunks (a page written in vain is simply written again) and no part
         keeps state of its own."""
         if self.graphs is None:
             return False
-        return all(need is None or (need.kind == "kv_pages" and not need.window) or need.kind == "none"
+        return all(need is None or (need.kind == "kv_pages" and not need.window and not need.chunk) or need.kind == "none"
                    for need in self.cache.needs)
 
     def launch_ahead(self, requests: Sequence[int], fed_ids: torch.Tensor) -> Optional[torch.Tensor]:
@@ -362,7 +364,7 @@ class Engine:
             bound *= 2
         return min(bound, self.max_context)
 
-    def _run(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+    def _run(self, entries: List[StepEntry], tap=None) -> Optional[torch.Tensor]:
         """A general step: any mix of portions of prompts and decoded tokens.
 
         The step's integers (token ids, positions, block tables, slots, and
@@ -407,7 +409,7 @@ class Engine:
         # contexts inside the bucket are.
         bound = self.context_bucket(longest)
         shape_key = (tuple(counts), len(wanted), bound, tuple(p.graph_key for p in prepared.values()))
-        graphed = self._step_graphs is not None and self.replay_general_steps and total <= self.step_graph_tokens and (
+        graphed = tap is None and self._step_graphs is not None and self.replay_general_steps and total <= self.step_graph_tokens and (
             shape_key in self._step_graphs or self._shapes_seen.get(shape_key, 0) >= 1)
         if graphed:   # the parts' integers and bounds for every step of this shape
             plan = StepPlan(counts, starts, rows, bound, replayable=True)
@@ -465,10 +467,10 @@ class Engine:
                 request_positions=None if graphed else starts, extras=extras)
             return self.model.forward(
                 d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),
-                d_wanted if wanted else None)
+                d_wanted if wanted else None, tap=tap)
 
         if not graphed:
-            if self._step_graphs is not None and self.replay_general_steps:
+            if tap is None and self._step_graphs is not None and self.replay_general_steps:
                 self._shapes_seen[shape_key] = self._shapes_seen.get(shape_key, 0) + 1
                 if len(self._shapes_seen) > 4096:
                     self._shapes_seen.clear()

@@ -7,9 +7,8 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .. import ops
 from ..config.spec import CacheNeed, ModelSpec
-from ..parts.registry import (CacheView, Runtime, StepContext, WeightStore, _BUILDERS, build_part)
+from ..parts.registry import (CacheView, Runtime, StepContext, WeightStore, _BUILDERS, build_part, settle)
 
 
 class DecoderModel:
@@ -57,21 +56,28 @@ class DecoderModel:
         """Bytes of every weight one step reads once."""
         total = self.head.weight_bytes() if not self.head.tied else self.embedding.weight_bytes()
         for block in self.blocks:
-            for part in (block.mixer, block.feed_forward):
+            for part in (block.mixer, getattr(block, "feed_forward", None)):
                 total += part.weight_bytes() if hasattr(part, "weight_bytes") else 0
         return total
 
-    def forward(self, token_ids: torch.Tensor, ctx: StepContext, views, wanted_rows: Optional[torch.Tensor]):
+    def forward(self, token_ids: torch.Tensor, ctx: StepContext, views, wanted_rows: Optional[torch.Tensor],
+                tap=None):
         """``views(entry, write) -> CacheView``. Returns float32 logits
-        [wanted, vocab], or None when no row is wanted."""
+        [wanted, vocab], or None when no row is wanted. ``tap(index, residual)``
+        is called after every layer run with the residual stream
+        ``[tokens, hidden]`` as that layer leaves it (the sums that otherwise
+        ride along into the next layer's first kernel are made at once then)."""
         residual = self.embedding.forward(token_ids)
         pending = None
-        for run in self.order:
+        for index, run in enumerate(self.order):
             block = self.blocks[run.layer]
             pending = block.forward(residual, pending, ctx, views(run.cache_entry(), run.write_cache))
+            if tap is not None:
+                settle(residual, pending)
+                pending = None
+                tap(index, residual)
         if wanted_rows is None or wanted_rows.numel() == 0:
             return None
-        if pending is not None:
-            ops.add_(residual, pending)
+        settle(residual, pending)
         normed = self.final_norm.forward(residual, self.runtime.dtype, rows_index=wanted_rows)
         return self.head.forward(normed)

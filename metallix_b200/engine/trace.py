@@ -36,8 +36,11 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     pages = -(-args.max_tokens // args.page_tokens)
+    # No request can hold more positions than the pool has: tables of positions
+    # and captured graphs are laid out for that many, not for a family's limit.
     engine = Engine.from_folder(args.model, dtype=args.dtype, page_tokens=args.page_tokens,
-                                num_pages=pages, max_requests=MAX_LIVE * 2)
+                                num_pages=pages, max_requests=MAX_LIVE * 2,
+                                max_context=pages * args.page_tokens)
     for line in sys.stdin:
         line = line.strip()
         if not line:

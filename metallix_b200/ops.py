@@ -34,21 +34,24 @@ _SIGNATURES = {
     "mxb_add": [_P, _P, _I, _L, _P],
     "mxb_copy_units": [_P, _I, _I, _L, _P, _I, _P, _P],
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
-                               _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
-    "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                               _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _I, _P, _P],
-    "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+    "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                                    _F, _I, _P, _P],
+    "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
+    "mxb_sigmoid_gate": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _P],
+    "mxb_softcap": [_P, _F, _L, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_decode_project_supported": [_I, _I, _I, _I, _I, _P, _L],
-    "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+    "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                                            _F, _P, _L, _I, _P, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
-    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
-    "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
+    "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
                                   _P, _P],
     "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
     "mxb_flash_prefill_tcgen05_tile": [],
@@ -305,6 +308,60 @@ def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
+def postnorm_add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
+                         next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                         out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x += RMSNorm(delta) * post_weight in float32 (in place); with
+    ``next_weight`` returns RMSNorm(x) * next_weight in ``out_dtype``, else
+    None. ``delta`` is ``[rows, size]``, or float32 ``[parts, rows, size]``
+    whose parts are added up first."""
+    _check(x, "x", (torch.float32,), 2)
+    _check(post_weight, "post_weight", (torch.float32,), 1)
+    rows, size = x.shape
+    _need(post_weight.numel() == size, "post_weight has the wrong size")
+    if delta.dim() == 3:
+        _check(delta, "delta", (torch.float32,), 3)
+        _need(delta.shape[1:] == x.shape and delta.shape[0] >= 1, "the summands and x differ in shape")
+        parts = delta.shape[0]
+    else:
+        _check(delta, "delta", tuple(_CODES), 2)
+        _need(delta.shape == x.shape, "delta and x differ in shape")
+        parts = 1
+    out = None
+    if next_weight is not None:
+        _check(next_weight, "next_weight", (torch.float32,), 1)
+        _need(next_weight.numel() == size and out_dtype in _CODES, "next_weight or out_dtype does not fit")
+        out = torch.empty((rows, size), dtype=out_dtype, device=x.device)
+    _call("mxb_postnorm_add_rmsnorm", x.data_ptr(), delta.data_ptr(), _CODES[delta.dtype], parts,
+          post_weight.data_ptr(), float(post_eps), _ptr(out), _CODES[out_dtype] if out is not None else 0,
+          _ptr(next_weight), float(next_eps), rows, size, _stream())
+    return out
+
+
+def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = a * sigmoid(gate), float32 inside; ``a`` and ``gate`` are
+    [rows, width] with unit column stride (rows may be strided: a column range
+    of a wider product)."""
+    for name, tensor in (("a", a), ("gate", gate)):
+        _need(tensor.is_cuda and tensor.dtype in _CODES and tensor.dim() == 2 and tensor.stride(1) == 1,
+              f"{name} must be a CUDA [rows, width] tensor with unit column stride")
+    _need(a.shape == gate.shape and a.dtype == gate.dtype, "a and gate differ in shape or dtype")
+    if out is None:
+        out = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    _need(out.shape == a.shape and out.dtype == a.dtype and out.stride(1) == 1, "out does not fit")
+    _call("mxb_sigmoid_gate", out.data_ptr(), a.data_ptr(), gate.data_ptr(), out.stride(0), a.stride(0),
+          gate.stride(0), a.shape[0], a.shape[1], _CODES[a.dtype], _stream())
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap), in place (float32)."""
+    _check(x, "x", (torch.float32,))
+    _need(cap > 0.0, "the cap must be positive")
+    _call("mxb_softcap", x.data_ptr(), float(cap), x.numel(), _stream())
+    return x
+
+
 # ------------------------------------------------------- copies in the cache
 def copy_units(pool: torch.Tensor, pairs: torch.Tensor) -> None:
     """pool[:, target] = pool[:, source] for every (source, target) row of
@@ -326,9 +383,13 @@ def qk_norm_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_out:
                        cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
                        positions: torch.Tensor, q_weight: Optional[torch.Tensor],
                        k_weight: Optional[torch.Tensor], cos: Optional[torch.Tensor],
-                       sin: Optional[torch.Tensor], eps: float) -> None:
-    """Per-head RMSNorm of q and k (if weights are given), rotate-half rotation
-    by ``positions`` (if tables are given), q written to ``q_out``
+                       sin: Optional[torch.Tensor], eps: float, interleaved: bool = False,
+                       norm_scope: str = "head") -> None:
+    """RMSNorm of q and k (if weights are given; ``norm_scope`` "head": each
+    head by itself, weights of head_dim values; "projection": all of a token's
+    query heads together and all of its key heads together, weights as wide as
+    the projections), rotation by ``positions`` (if tables are given; pairs
+    (i, i + rotary_dim / 2), or (2i, 2i + 1) when ``interleaved``), q written to ``q_out``
     [tokens, heads, head_dim], k and v written into ``cache``
     [pages, 2, kv_heads, page_tokens, head_dim] at ``slots`` (a negative slot
     skips the token; ``cache=None`` writes nothing). q, k and v are
@@ -357,10 +418,14 @@ def qk_norm_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_out:
     if q_out is not None:
         _check(q_out, "q_out", (dtype,), 3)
         _need(q_out.shape == (tokens, heads, head_dim), "q_out must be [tokens, heads, head_dim]")
-    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+    _need(norm_scope in ("head", "projection"), f"unknown norm scope {norm_scope!r}")
+    for name, weight, width in (("q_weight", q_weight, heads * head_dim), ("k_weight", k_weight, kv_heads * head_dim)):
         if weight is not None:
             _check(weight, name, (torch.float32,), 1)
-            _need(weight.numel() == head_dim, f"{name} must have head_dim values")
+            if norm_scope == "head":
+                _need(weight.numel() == head_dim, f"{name} must have head_dim values")
+            else:
+                _need(weight.numel() == width, f"{name} must have {width} values, one per value of the projection")
     rotary_dim, table_positions = 0, 0
     if cos is not None:
         _check(cos, "cos", (torch.float32,), 2)
@@ -370,20 +435,23 @@ def qk_norm_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_out:
         _need(rotary_dim <= head_dim, "rotary_dim exceeds head_dim")
     _call("mxb_qk_norm_rope_cache", q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0),
           v.stride(0), _ptr(q_out), _ptr(cache), _ptr(slots), positions.data_ptr(), _ptr(q_weight),
-          _ptr(k_weight), _ptr(cos), _ptr(sin), table_positions, rotary_dim, tokens, heads, kv_heads,
+          _ptr(k_weight), _ptr(cos), _ptr(sin), table_positions, rotary_dim, 1 if interleaved else 0,
+          1 if norm_scope == "projection" else 0, tokens, heads, kv_heads,
           head_dim, page_tokens, num_pages, float(eps), _CODES[dtype],
           status_word(q.device).data_ptr(), _stream())
 
 
 def norm_rotate_heads(x: torch.Tensor, head_dim: int, positions: torch.Tensor,
                       weight: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
-                      sin: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
-    """Per-head RMSNorm (if ``weight``) and rotation (if tables) of x
+                      sin: Optional[torch.Tensor] = None, eps: float = 0.0, interleaved: bool = False,
+                      norm_scope: str = "head") -> torch.Tensor:
+    """RMSNorm (if ``weight``) and rotation (if tables) of x
     [tokens, n * head_dim]; returns [tokens, n, head_dim]. Writes no cache."""
     _need(x.dim() == 2 and x.shape[1] % head_dim == 0, "x must be [tokens, n * head_dim]")
     out = torch.empty((x.shape[0], x.shape[1] // head_dim, head_dim), dtype=x.dtype, device=x.device)
     empty = x[:, :0]
-    qk_norm_rope_cache(x, empty, empty, out, None, None, positions, weight, None, cos, sin, eps)
+    qk_norm_rope_cache(x, empty, empty, out, None, None, positions, weight, None, cos, sin, eps,
+                       interleaved=interleaved, norm_scope=norm_scope)
     return out
 
 
@@ -397,9 +465,11 @@ def write_cache(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slots: to
 def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor,
                          block_tables: torch.Tensor, tile_request: torch.Tensor,
                          tile_start: torch.Tensor, tile_length: torch.Tensor,
-                         positions: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
+                         positions: torch.Tensor, scale: float, window: int = 0, chunk: int = 0) -> torch.Tensor:
     """Attention of every query token over its request's cached keys (itself
-    included) in float32; q and out are [tokens, heads, head_dim]."""
+    included) in float32; q and out are [tokens, heads, head_dim]. ``window``:
+    only the last that many positions are seen; ``chunk``: only the keys of the
+    query's own chunk of that many positions, counted from position 0."""
     dtype = q.dtype
     _check(q, "q", tuple(_CODES), 3)
     _check(out, "out", (dtype,), 3)
@@ -420,7 +490,7 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     _call("mxb_paged_attention_tile", q.data_ptr(), cache.data_ptr(), out.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(),
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
-          kv_heads, head_dim, page_tokens, num_pages, int(window or 0), float(scale), _CODES[dtype],
+          kv_heads, head_dim, page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[dtype],
           status_word(q.device).data_ptr(), _stream())
     return out
 
@@ -451,7 +521,7 @@ def flash_prefill_tcgen05_supported(head_dim: int, heads: int, kv_heads: int, pa
 KEY_SHARES = None   # an int forces the number of blocks that share a query tile's keys (tests, comparisons)
 
 
-def flash_key_shares(blocks: int, longest_context: int, window: int = 0) -> int:
+def flash_key_shares(blocks: int, longest_context: int, window: int = 0, chunk: int = 0) -> int:
     """How many blocks share the keys of a query tile of the tcgen05 prompt
     kernel: one, unless the step has so few (tile, head) blocks and so many
     keys that most SMs would stand idle (a portion of a prompt behind a long
@@ -459,6 +529,8 @@ def flash_key_shares(blocks: int, longest_context: int, window: int = 0) -> int:
     if KEY_SHARES is not None:
         return max(1, int(KEY_SHARES))
     keys = min(longest_context, window) if window else longest_context
+    if chunk:
+        keys = min(keys, chunk)
     if blocks >= 100 or keys < 2048:
         return 1
     return max(1, min(8, 148 // blocks, keys // 1024))
@@ -467,7 +539,7 @@ def flash_key_shares(blocks: int, longest_context: int, window: int = 0) -> int:
 def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
                   positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto",
-                  longest_context: int = 0) -> torch.Tensor:
+                  longest_context: int = 0, chunk: int = 0) -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
     float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
     of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
@@ -499,14 +571,14 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
           f"the tcgen05 prompt kernel does not take head_dim {head_dim} with pages of {page_tokens} tokens")
     if tcgen05 and kernel != "mma":
         _need(q.is_contiguous() and cache.is_contiguous(), "q and cache must be contiguous")
-        shares = flash_key_shares(tiles * heads, int(longest_context), int(window or 0))
+        shares = flash_key_shares(tiles * heads, int(longest_context), int(window or 0), int(chunk or 0))
         partial = None
         if shares > 1:
             partial = torch.empty(tokens * heads * shares * (head_dim + 2), dtype=torch.float32, device=q.device)
         _call("mxb_flash_prefill_tcgen05", q.data_ptr(), cache.data_ptr(), out.data_ptr(),
               block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
               tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
-              page_tokens, num_pages, int(window or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
+              page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
               status_word(q.device).data_ptr(), _stream())
         if shares > 1:
             global _launches
@@ -515,7 +587,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     _call("mxb_flash_prefill", q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
           positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,
-          int(window or 0), float(scale), _CODES[q.dtype], status_word(q.device).data_ptr(), _stream())
+          int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -545,7 +617,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
                            block_tables: torch.Tensor, row_token: torch.Tensor,
                            row_request: torch.Tensor, positions: torch.Tensor, scale: float,
                            longest_context: int, window: int = 0,
-                           partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           partial: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
     """Attention of single tokens over their requests' cached keys, split
     along the keys. ``row_token[i]`` is the token (row of q and out) of the
     i-th decoded request, negative for a padding row; ``row_request[i]`` its
@@ -576,7 +648,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
     _call("mxb_paged_attention_decode", q.data_ptr(), cache.data_ptr(), out.data_ptr(), partial.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
-          int(window or 0), float(scale), _CODES[dtype], status_word(q.device).data_ptr(), _stream())
+          int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -592,7 +664,7 @@ def decode_project_supported(head_dim: int, heads: int, kv_heads: int, dtype: to
 def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                                    row_token: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor,
                                    scale: float, longest_context: int, weight: torch.Tensor,
-                                   window: int = 0) -> torch.Tensor:
+                                   window: int = 0, chunk: int = 0) -> torch.Tensor:
     """``paged_attention_decode`` followed at once by the output projection
     ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 64 tokens in
     bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
@@ -617,7 +689,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
     _call("mxb_paged_attention_decode_project", q.data_ptr(), cache.data_ptr(), partial.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, tokens, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
-          int(window or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
+          int(window or 0), int(chunk or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
           status_word(q.device).data_ptr(), _stream())
     return summands
 

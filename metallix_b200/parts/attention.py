@@ -6,6 +6,14 @@ a causal mask (and an optional window), softmax over keys, query head j reading
 key/value head j // (heads / kv_heads); then the output projection
 (crates/models/qwen/src/forward.rs:2012-2065, :1967-1989, :2070-2093).
 
+Variants, each a parameter: the norms of q and k may run over a token's whole
+projection instead of head by head (``qk_norm_scope="projection"``); a model
+without a value projection takes its values from the keys as projected, before
+norm and rotation (no ``v_proj``); ``chunk`` lets a query see only the keys of
+its own chunk of that many positions, counted from position 0 of the sequence;
+``gate_proj`` multiplies the concatenated heads by sigmoid(a Wg^T) ahead of the
+output projection.
+
 Every size and constant is a parameter. When the head norms are RMSNorms (or
 absent) and the position encoding offers cos/sin tables (or is absent), norm,
 rotation and cache write run as one kernel; any other norm or position part is
@@ -110,24 +118,44 @@ class GQAttention:
         self.head_dim = spec["head_dim"]
         self.scale = float(spec["scale"])
         self.window = spec.get("window") or 0
+        self.chunk = spec.get("chunk") or 0
+        self.norm_scope = spec.get("qk_norm_scope") or "head"
+        if self.norm_scope not in ("head", "projection"):
+            raise ValueError(f"qk_norm_scope must be 'head' or 'projection', got {self.norm_scope!r}")
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} query heads cannot share {self.num_kv_heads} key/value heads")
         if self.head_dim % 2 or not 0 < self.head_dim <= 256:
             raise ValueError(f"head_dim {self.head_dim}: the attention kernels take even sizes up to 256")
-        q, k, v = (weights.take(spec[name]) for name in ("q_proj", "k_proj", "v_proj"))
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
-        for name, weight, rows in (("q_proj", q, self.q_size), ("k_proj", k, self.kv_size),
-                                   ("v_proj", v, self.kv_size)):
+        # v_proj absent: the values are the keys as projected. gate_proj: an
+        # output gate over the concatenated heads, from the mixer's own input.
+        self.own_values = spec.get("v_proj") is not None
+        self.gated = spec.get("gate_proj") is not None
+        stacked = []
+        for name, rows, present in (("q_proj", self.q_size, True), ("k_proj", self.kv_size, True),
+                                    ("v_proj", self.kv_size, self.own_values),
+                                    ("gate_proj", self.q_size, self.gated)):
+            if not present:
+                continue
+            weight = weights.take(spec[name])
             if tuple(weight.shape) != (rows, self.hidden_size):
                 raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {(rows, self.hidden_size)}")
-        self.qkv = Linear.stacked([q, k, v], runtime)  # rows: all q heads, then k heads, then v heads
+            stacked.append(weight)
+        # rows: all q heads, then k heads, then v heads (if any), then the gate (if any)
+        self.qkv = Linear.stacked(stacked, runtime)
+        self.gate_offset = self.q_size + self.kv_size * (2 if self.own_values else 1)
         self.o = Linear(weights.take(spec["o_proj"]), runtime)
         if (self.o.out_features, self.o.in_features) != (self.hidden_size, self.q_size):
             raise ValueError(f"{spec['o_proj']} is {tuple(self.o.weight.shape)}")
         self.q_norm = build_part("norm", spec.get("q_norm"), weights, runtime)
         self.k_norm = build_part("norm", spec.get("k_norm"), weights, runtime)
         self.position = build_part("position", spec.get("position"), weights, runtime)
+        for name, norm, width in (("q_norm", self.q_norm, self.q_size), ("k_norm", self.k_norm, self.kv_size)):
+            expected = self.head_dim if self.norm_scope == "head" else width
+            if norm is not None and getattr(norm, "size", expected) != expected:
+                raise ValueError(f"{name} is over {norm.size} values; with qk_norm_scope {self.norm_scope!r} "
+                                 f"it must be over {expected}")
         norms_fuse = all(n is None or isinstance(n, RMSNorm) for n in (self.q_norm, self.k_norm))
         eps_agree = (self.q_norm is None or self.k_norm is None or self.q_norm.eps == self.k_norm.eps)
         position_fuses = self.position is None or getattr(self.position, "fused_tables", False)
@@ -140,7 +168,7 @@ class GQAttention:
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kind="kv_pages", kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                         window=self.window or None)
+                         window=self.window or None, chunk=self.chunk or None)
 
     def parts(self):
         return [self.q_norm, self.k_norm, self.position]
@@ -176,7 +204,9 @@ class GQAttention:
         qkv = self.qkv.forward(x)
         q = qkv[:, :self.q_size]
         k = qkv[:, self.q_size:self.q_size + self.kv_size]
-        v = qkv[:, self.q_size + self.kv_size:]
+        v = qkv[:, self.q_size + self.kv_size:self.q_size + 2 * self.kv_size] if self.own_values else k
+        gate = qkv[:, self.gate_offset:self.gate_offset + self.q_size] if self.gated else None
+        per_head = self.norm_scope == "head"
         q_heads = torch.empty((tokens, self.num_heads, self.head_dim), dtype=self.dtype, device=x.device)
         write = cache.write and cache.slots is not None
         if self.fused:
@@ -187,14 +217,17 @@ class GQAttention:
                 self.q_norm.weight if self.q_norm is not None else None,
                 self.k_norm.weight if self.k_norm is not None else None,
                 self.position.cos if self.position is not None else None,
-                self.position.sin if self.position is not None else None, eps)
+                self.position.sin if self.position is not None else None, eps,
+                interleaved=bool(getattr(self.position, "interleaved", False)), norm_scope=self.norm_scope)
         else:
+            if not self.own_values:
+                v = k   # as projected: before the norm and the rotation below
             if self.q_norm is not None:
-                q = self.q_norm.forward(q.reshape(tokens * self.num_heads, self.head_dim).contiguous(),
-                                        self.dtype).view(tokens, self.q_size)
+                rows = (tokens * self.num_heads, self.head_dim) if per_head else (tokens, self.q_size)
+                q = self.q_norm.forward(q.reshape(rows).contiguous(), self.dtype).view(tokens, self.q_size)
             if self.k_norm is not None:
-                k = self.k_norm.forward(k.reshape(tokens * self.num_kv_heads, self.head_dim).contiguous(),
-                                        self.dtype).view(tokens, self.kv_size)
+                rows = (tokens * self.num_kv_heads, self.head_dim) if per_head else (tokens, self.kv_size)
+                k = self.k_norm.forward(k.reshape(rows).contiguous(), self.dtype).view(tokens, self.kv_size)
             if self.position is not None:
                 q_rot, k_rot = self.position.apply(q, k, ctx.positions)
                 q_heads = q_rot.contiguous().view(tokens, self.num_heads, self.head_dim)
@@ -207,33 +240,37 @@ class GQAttention:
         multi_tiles = tiles["multi_tiles"]
         split = tiles["decode_rows"] and self.split_decode
         if (summands and split and multi_tiles == 0 and tokens <= PROJECT_TOKENS and self.o.rows_are_short()
+                and not self.gated
                 and ops.decode_project_supported(self.head_dim, self.num_heads, self.num_kv_heads, self.dtype,
                                                  tokens, self.o.weight)):
             # Only single tokens, at most 64 of them: the splits are merged
             # and projected by one kernel, one summand per head.
             return ops.paged_attention_decode_project(
                 q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
-                ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window)
+                ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window, self.chunk)
         out = torch.empty_like(q_heads)
         if split:
             # Requests that bring one token: split along the keys.
             ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],
                                        tiles["decode_request"], ctx.positions, self.scale,
-                                       tiles["longest_context"], self.window)
+                                       tiles["longest_context"], self.window, chunk=self.chunk)
         if self.flash:
             # Requests that bring several tokens: tensor cores, tiles of 128.
             if tiles["wide_request"].numel():
                 ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, tiles["wide_request"],
                                   tiles["wide_start"], tiles["wide_length"], ctx.positions, self.scale,
-                                  self.window, longest_context=tiles["longest_keys"])
+                                  self.window, longest_context=tiles["longest_keys"], chunk=self.chunk)
             rest = None if split else slice(multi_tiles, None)   # single tokens not yet served
         else:
             rest = slice(0, multi_tiles) if split else slice(0, None)
         if rest is not None and tiles["tile_request"][rest].numel():
             ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, tiles["tile_request"][rest],
                                      tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
-                                     self.scale, self.window)
-        return self.o.forward(out.view(tokens, self.q_size))
+                                     self.scale, self.window, self.chunk)
+        heads_out = out.view(tokens, self.q_size)
+        if gate is not None:
+            ops.sigmoid_gate(heads_out, gate, out=heads_out)
+        return self.o.forward(heads_out)
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()

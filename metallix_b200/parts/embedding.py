@@ -1,7 +1,8 @@
 """The model's two ends: token embedding (row gather,
 crates/models/qwen/src/forward/projection.rs:208-216) and the output head
 (logits = n W^T through the embedding when tied, else lm_head,
-crates/models/qwen/src/forward.rs:574-580), whose logits leave in float32."""
+crates/models/qwen/src/forward.rs:574-580), whose logits leave in float32;
+with ``softcap`` c they are bounded to (-c, c): c tanh(logits / c)."""
 from __future__ import annotations
 
 import torch
@@ -48,9 +49,13 @@ class LinearHead:
             self.tied = False
         if self.linear.out_features != spec["vocab_size"] or self.linear.in_features != spec["hidden_size"]:
             raise ValueError(f"{spec['weight']} is {tuple(self.linear.weight.shape)}")
+        self.softcap = float(spec.get("softcap") or 0.0)
+        if self.softcap < 0.0:
+            raise ValueError(f"softcap must be positive, got {self.softcap}")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.linear.forward(x, out_dtype=torch.float32)
+        logits = self.linear.forward(x, out_dtype=torch.float32)
+        return ops.softcap_(logits, self.softcap) if self.softcap else logits
 
     def weight_bytes(self) -> int:
         return 0 if self.tied else self.linear.weight_bytes()

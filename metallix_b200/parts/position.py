@@ -1,13 +1,26 @@
-"""Rotate-half rotary position encoding over the first ``rotary_dim`` values
-of a head (crates/models/qwen/src/forward.rs:2031-2054: dims = head_dim,
-traditional = false, base = rope_theta, scale 1). For i < rotary_dim / 2:
-f_i = theta^(-2i / rotary_dim), out[i] = x[i] cos(p f_i) - x[i + half] sin(p f_i),
-out[i + half] = x[i + half] cos(p f_i) + x[i] sin(p f_i).
+"""Rotary position encodings over the first ``rotary_dim`` values of a head.
+
+``rope_half`` pairs value i with value i + rotary_dim / 2
+(crates/models/qwen/src/forward.rs:2031-2054: dims = head_dim, traditional =
+false, base = rope_theta, scale 1); ``rope_interleaved`` pairs value 2i with
+value 2i + 1. Either way pair i at position p turns by the angle p f_i,
+f_i = theta^(-2i / rotary_dim): (a, b) -> (a cos - b sin, b cos + a sin); the
+values beyond ``rotary_dim`` pass unchanged.
+
+``scaling`` (optional) stretches the long wavelengths for contexts beyond
+those a model was trained on, by a rule of three bands over the wavelength
+l_i = 2 pi / f_i: with ``original`` positions, a ``factor`` and the two band
+edges ``low`` < ``high``, a frequency is kept where l_i < original / high,
+divided by ``factor`` where l_i > original / low, and in between blended,
+(1 - s) f_i / factor + s f_i with s = (original / l_i - low) / (high - low).
 
 Angles are formed in float64 (position times frequency), cos and sin are
 rounded once to float32 tables that the kernels index by position.
 """
 from __future__ import annotations
+
+import math
+from typing import Mapping, Optional
 
 import torch
 
@@ -16,21 +29,45 @@ from ..config.spec import PartSpec
 from .registry import Runtime, WeightStore, register_part
 
 
-class RotaryHalf:
-    kind = "rope_half"
-    fused_tables = True  # the attention mixer may hand cos/sin to its fused kernel
+def rotary_frequencies(theta: float, rotary_dim: int, scaling: Optional[Mapping] = None) -> torch.Tensor:
+    """float64 ``[rotary_dim / 2]``: f_i = theta^(-2i / rotary_dim), stretched by
+    ``scaling`` (factor, low, high, original) as described above."""
+    index = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    frequency = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * index / rotary_dim)
+    if scaling:
+        factor, low, high = float(scaling["factor"]), float(scaling["low"]), float(scaling["high"])
+        original = float(scaling["original"])
+        if not (factor > 0.0 and high > low and original > 0.0):
+            raise ValueError(f"rotary scaling needs factor > 0, high > low and original > 0, got {dict(scaling)}")
+        wavelength = 2.0 * math.pi / frequency
+        blend = (original / wavelength - low) / (high - low)
+        between = (1.0 - blend) * frequency / factor + blend * frequency
+        frequency = torch.where(wavelength < original / high, frequency,
+                                torch.where(wavelength > original / low, frequency / factor, between))
+    return frequency
 
-    def __init__(self, theta: float, rotary_dim: int, head_dim: int, runtime: Runtime):
+
+def _scaling_key(scaling: Optional[Mapping]) -> tuple:
+    return tuple(sorted((str(k), float(v)) for k, v in scaling.items())) if scaling else ()
+
+
+class Rotary:
+    """Both pairings; ``interleaved`` says which."""
+
+    fused_tables = True  # the attention mixer may hand cos/sin to its fused kernel
+    interleaved = False
+
+    def __init__(self, theta: float, rotary_dim: int, head_dim: int, runtime: Runtime,
+                 scaling: Optional[Mapping] = None):
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and within head_dim {head_dim}")
         self.theta, self.rotary_dim, self.head_dim = float(theta), rotary_dim, head_dim
-        # Layers with the same parameters share one pair of tables.
-        key = ("rope_half", self.theta, rotary_dim, runtime.max_positions, str(runtime.device))
+        self.scaling = dict(scaling) if scaling else None
+        # Layers with the same parameters share one pair of tables (the pairing
+        # does not enter: pair i has the same angle in both).
+        key = ("rope", self.theta, rotary_dim, _scaling_key(self.scaling), runtime.max_positions, str(runtime.device))
         if key not in runtime.shared:
-            half = rotary_dim // 2
-            index = torch.arange(half, dtype=torch.float64, device=runtime.device)
-            frequency = torch.pow(torch.tensor(self.theta, dtype=torch.float64, device=runtime.device),
-                                  -2.0 * index / rotary_dim)
+            frequency = rotary_frequencies(self.theta, rotary_dim, self.scaling).to(runtime.device)
             position = torch.arange(runtime.max_positions, dtype=torch.float64, device=runtime.device)
             angle = position[:, None] * frequency[None, :]
             runtime.shared[key] = (torch.cos(angle).to(torch.float32).contiguous(),
@@ -40,13 +77,27 @@ class RotaryHalf:
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor):
         """Rotates q [tokens, heads * head_dim] and k [tokens, kv_heads * head_dim];
         returns (q_rotated [tokens, heads, head_dim], k_rotated [tokens, kv_heads, head_dim])."""
-        q_out = ops.norm_rotate_heads(q, self.head_dim, positions, cos=self.cos, sin=self.sin)
-        k_out = ops.norm_rotate_heads(k, self.head_dim, positions, cos=self.cos, sin=self.sin)
+        q_out = ops.norm_rotate_heads(q, self.head_dim, positions, cos=self.cos, sin=self.sin,
+                                      interleaved=self.interleaved)
+        k_out = ops.norm_rotate_heads(k, self.head_dim, positions, cos=self.cos, sin=self.sin,
+                                      interleaved=self.interleaved)
         return q_out, k_out
 
 
-def _build(spec: PartSpec, weights: WeightStore, runtime: Runtime) -> RotaryHalf:
-    return RotaryHalf(spec["theta"], spec["rotary_dim"], spec["head_dim"], runtime)
+class RotaryHalf(Rotary):
+    kind = "rope_half"
 
 
-register_part("position", "rope_half", _build)
+class RotaryInterleaved(Rotary):
+    kind = "rope_interleaved"
+    interleaved = True
+
+
+def _builder(cls):
+    def build(spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        return cls(spec["theta"], spec["rotary_dim"], spec["head_dim"], runtime, scaling=spec.get("scaling"))
+    return build
+
+
+register_part("position", "rope_half", _builder(RotaryHalf))
+register_part("position", "rope_interleaved", _builder(RotaryInterleaved))

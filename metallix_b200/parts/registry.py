@@ -105,6 +105,29 @@ class CacheView:
 
 
 @dataclass
+class Pending:
+    """A sublayer's output that has not joined the residual stream yet, for an
+    arrangement in which it passes a norm of its own first: whoever adds it
+    computes residual += norm(delta). A norm part's ``add_forward`` takes a
+    ``Pending`` wherever it takes a plain tensor (``delta`` may be float32
+    ``[parts, rows, size]`` summands there too)."""
+
+    delta: torch.Tensor
+    norm: object
+
+
+def settle(residual: torch.Tensor, pending) -> None:
+    """Adds what a block left pending to the residual stream (float32, in place)."""
+    from .. import ops
+    if pending is None:
+        return
+    if isinstance(pending, Pending):
+        pending.norm.add_normed(residual, pending.delta)
+    else:
+        ops.add_(residual, pending)
+
+
+@dataclass
 class StepPlan:
     """A step as the host knows it, handed to the parts that keep integers
     of their own for it (``prepare_step``): request row r brings

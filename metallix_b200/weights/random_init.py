@@ -5,7 +5,8 @@ The reference has only test-local generators (an arithmetic pattern at
 ``crates/models/qwen/src/forward.rs:4548-4555``, an LCG at
 ``forward/tests/paged_kv.rs:49-128`` with norm weights near one). Here linear
 and embedding weights are drawn from N(0, 0.02) and every norm weight,
-q/k-norms included, from 1 + U(-0.1, 0.1).
+q/k-norms included, from 1 + U(-0.1, 0.1) (U(-0.1, 0.1) where a family
+stores the factor minus one).
 
 The generator is counter-based, as the reference's sampling noise is
 (Philox4x32-10, ``crates/core/engine/src/sampling/race.rs:40-86``): element
@@ -146,8 +147,10 @@ def random_tensors(config, seed: int, dtype: str = "bfloat16", device: str = "cp
     vector_dtype = _DTYPES[norm_dtype or dtype]
     tensors: Dict[str, torch.Tensor] = {}
     for name, shape in config.tensor_shapes().items():
-        norm = bool(config.norm_tensor(name))
-        value = random_tensor(seed, name, shape, norm, device)
+        norm = config.norm_tensor(name)   # False, True / "one" (a factor near 1) or "zero" (stored as factor - 1)
+        value = random_tensor(seed, name, shape, bool(norm), device)
+        if norm == "zero":
+            value = value - 1.0
         tensors[name] = value.to(vector_dtype if norm else matrix_dtype)
     return tensors
 
