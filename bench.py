@@ -5,6 +5,7 @@
     python bench.py --shape 8b                                    continuous batching of 64 requests
     python bench.py --shape 32b                                   prefill and decode at 8,192-token contexts
     python bench.py --workload decode|prefill|gemm|attention|pick ...   small fixed workloads for profilers
+    python bench.py --design mekazen                              the Mekazen decoder beside Qwen3 at equal layer sizes
 
 Default workload: a Qwen3-0.6B-shaped model (28 layers,
 hidden 1024, 16 query and 8 key/value heads of 128, SwiGLU 3072, vocabulary
@@ -714,6 +715,150 @@ def workload(args):
     return 0
 
 
+# ------------------------------------------------- another design, side by side
+# Layer sizes (hidden, query heads, key/value heads, head size, feed-forward) of
+# the 0.6B- and 8B-shaped models, 8 layers each, vocabulary 32,768.
+DESIGN_SIZES = {"0.6b-layers": (1024, 16, 8, 128, 3072), "8b-layers": (4096, 32, 8, 128, 12288)}
+DESIGN_LAYERS, DESIGN_VOCAB = 8, 32768
+
+
+def _mekazen(hidden, heads, kv_heads, dim, inter, chunk):
+    mixer = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": chunk}, "scale": dim ** -0.5,
+             "vdim": dim, "rot": {"base": 1.0e6, "dims": dim // 2,
+                                  "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    layer = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": inter}}
+    return {"architecture": "Mekazen", "vocab": DESIGN_VOCAB, "width": hidden, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": [layer] * DESIGN_LAYERS}
+
+
+def design(args):
+    """Prompt and decode throughput of the Mekazen decoder beside the Qwen3
+    decoder with the same layer sizes (random weights, bfloat16), and each
+    kernel the design adds beside the like kernel of Qwen3 on the same rows,
+    as bytes moved over time against the measured copy bandwidth. One JSON
+    line. The chunk (``--chunk``) is as long as the contexts by default, so
+    that both models' attention does the same work."""
+    import numpy as np
+    import torch
+    from metallix_b200 import ops, parse_config
+    from metallix_b200.engine import Engine, StepEntry
+
+    peak, peak_source = peaks()
+    warmup, steps = max(args.warmup, 3), min(max(args.steps, 1), 64)
+    rng = np.random.default_rng(0)
+    out = {"design": "mekazen", "beside": "qwen3", "dtype": "bf16", "layers": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
+           "prompt_len": args.prompt_len, "chunk": args.chunk or args.context, "peaks": peak_source, "sizes": {}}
+    for size, (hidden, heads, kv_heads, dim, inter) in DESIGN_SIZES.items():
+        configs = {
+            "mekazen": parse_config(_mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or args.context)),
+            "qwen3": parse_config(dict(_qwen3(DESIGN_LAYERS, hidden, heads, kv_heads, inter, False),
+                                       vocab_size=DESIGN_VOCAB, head_dim=dim))}
+        row = {}
+        for family, config in configs.items():
+            span = args.prompt_len + warmup + steps + 64
+            engine = Engine.from_random(config, seed=0, dtype="bfloat16", page_tokens=16,
+                                        num_pages=8 * (-(-span // 16)) + 64, max_requests=10,
+                                        max_context=args.context, gemm_backend=args.gemm)
+            device = engine.device
+
+            def one_prefill(tokens):
+                engine.step([StepEntry("prefill", tokens, [len(tokens) - 1])])
+                engine.release("prefill")
+
+            prompt = rng.integers(0, DESIGN_VOCAB, size=args.prompt_len).tolist()
+            for _ in range(4):   # launched kernel by kernel, seen, captured, replayed
+                one_prefill(prompt)
+            prefill_ms = statistics.median(timed(torch, device, lambda _: one_prefill(prompt), 1) for _ in range(5))
+            result = {"prefill_ms": prefill_ms, "prefill_tok_s": args.prompt_len / prefill_ms * 1e3}
+            for batch in (1, 8):
+                engine.release_all()
+                names = [f"r{i}" for i in range(batch)]
+                for first in range(0, batch, 4):
+                    engine.step([StepEntry(n, rng.integers(0, DESIGN_VOCAB, size=args.prompt_len).tolist(), [])
+                                 for n in names[first:first + 4]])
+                feed = rng.integers(0, DESIGN_VOCAB, size=(warmup + 3 * steps, batch))
+
+                def one(index):
+                    engine.step([StepEntry(n, [int(feed[index, i])], [0]) for i, n in enumerate(names)])
+
+                for index in range(warmup):
+                    one(index)
+                before = ops.launch_count()
+                runs = sorted(timed(torch, device, lambda index: one(warmup + r * steps + index), steps)
+                              for r in range(3))
+                launches = (ops.launch_count() - before) // 3
+                ms = runs[1] / steps
+                step_bytes = engine.model.weight_bytes() + batch * (args.prompt_len + warmup + 1.5 * steps) \
+                    * engine.cache.bytes_per_token()
+                result[f"decode_b{batch}"] = {
+                    "ms_per_step": ms, "tok_s": batch / ms * 1e3, "kernels_per_step": launches // steps,
+                    "frac_of_copy_bandwidth": step_bytes / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
+            engine.check()
+            row[family] = result
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+
+    # ---- the kernels the design adds, beside their like, on one layer's rows
+    def gbs(bytes_moved, function):
+        for _ in range(3):
+            function()
+        flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+        times = []
+        for _ in range(7):
+            flush.zero_()    # a buffer larger than L2 between the timed launches
+            times.append(timed(torch, "cuda", lambda _: function(), 1))
+        ms = statistics.median(times)
+        return {"us": ms * 1e3, "gb_s": bytes_moved / (ms * 1e-3) / 1e9,
+                "frac_of_copy_bandwidth": bytes_moved / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
+
+    kernels = {}
+    hidden, heads, kv_heads, dim, inter = DESIGN_SIZES["8b-layers"]
+    bf16 = torch.bfloat16
+    for tokens in (8, args.prompt_len * 4):
+        x = torch.randn(tokens, hidden, device="cuda")
+        delta = torch.randn(tokens, hidden, device="cuda").to(bf16)
+        weight = torch.ones(hidden, device="cuda")
+        moved = tokens * hidden * (4 + 4 + 2 + 2)   # x read and written, the delta read, the output written
+        kernels[f"norm_sum_norm_{tokens}"] = {
+            "mekazen: x += norm(d); y = norm(x)": gbs(moved, lambda: ops.postnorm_add_rmsnorm(
+                x, delta, weight, 1e-6, weight, 1e-6, bf16)),
+            "qwen3: x += d; y = norm(x)": gbs(moved, lambda: ops.add_rmsnorm(x, delta, weight, 1e-6, bf16))}
+        q_size, kv_size = heads * dim, kv_heads * dim
+        qkv = torch.randn(tokens, q_size + 2 * kv_size, device="cuda").to(bf16)
+        q_out = torch.empty(tokens, heads, dim, dtype=bf16, device="cuda")
+        pages = -(-tokens // 16)
+        cache = torch.zeros(pages, 2, kv_heads, 16, dim, dtype=bf16, device="cuda")
+        slots = torch.arange(tokens, dtype=torch.int32, device="cuda")
+        positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+        cos = torch.ones(tokens, dim // 2, device="cuda")
+        sin = torch.zeros(tokens, dim // 2, device="cuda")
+        moved = tokens * (q_size + 2 * kv_size) * 2 * 2
+        q, k, v = qkv[:, :q_size], qkv[:, q_size:q_size + kv_size], qkv[:, q_size + kv_size:]
+        row_weights = (torch.ones(q_size, device="cuda"), torch.ones(kv_size, device="cuda"))
+        head_weight = torch.ones(dim, device="cuda")
+        kernels[f"qk_norm_rotation_cache_{tokens}"] = {
+            "mekazen: norm over the projection, pairs, a quarter of the head rotated": gbs(
+                moved, lambda: ops.qk_norm_rope_cache(q, k, k, q_out, cache, slots, positions, row_weights[0],
+                                                      row_weights[1], cos[:, :dim // 8].contiguous(),
+                                                      sin[:, :dim // 8].contiguous(), 1e-6, interleaved=True,
+                                                      norm_scope="projection")),
+            "qwen3: norm per head, halves, the whole head rotated": gbs(
+                moved, lambda: ops.qk_norm_rope_cache(q, k, v, q_out, cache, slots, positions, head_weight,
+                                                      head_weight, cos, sin, 1e-6))}
+        heads_out = torch.randn(tokens, q_size, device="cuda").to(bf16)
+        gate = torch.randn(tokens, q_size, device="cuda").to(bf16)
+        gate_up = torch.randn(tokens, 2 * q_size, device="cuda").to(bf16)
+        kernels[f"output_gate_{tokens}"] = {
+            "mekazen: out * sigmoid(gate)": gbs(tokens * q_size * 2 * 3,
+                                                lambda: ops.sigmoid_gate(heads_out, gate, out=heads_out)),
+            "qwen3: silu(gate) * up, the like elementwise kernel": gbs(tokens * q_size * 2 * 3,
+                                                                       lambda: ops.silu_mul(gate_up))}
+    out["kernels"] = kernels
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -752,6 +897,9 @@ def main():
     parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
     parser.add_argument("--page-tokens", type=int, default=16, help="workloads: tokens per cache page")
     parser.add_argument("--max-context", type=int, default=0, help="workloads: the engine's context limit")
+    parser.add_argument("--design", choices=("mekazen",),
+                        help="another decoder design beside Qwen3 at equal layer sizes, and its kernels beside their like")
+    parser.add_argument("--chunk", type=int, default=0, help="--design: positions per chunk of the mask (0: the context)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -763,6 +911,8 @@ def main():
     if args.decode_resident is not None:
         from metallix_b200 import ops
         ops.set_decode_resident_blocks(args.decode_resident, max(args.decode_many, args.decode_resident))
+    if args.design:
+        return design(args)
     if args.workload:
         return workload(args)
     if args.shape == "8b":

@@ -931,7 +931,7 @@ __global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
                              int rows, int heads, int head_dim, int max_splits, int window, int chunk, int slots,
-                             int* status) {
+                             const T* __restrict__ gate, long long gate_stride, int* status) {
   chain_release();
   const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
@@ -978,7 +978,14 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
     }
     m = round_max;
   }
-  out[(static_cast<size_t>(token) * heads + head) * head_dim + d] = from_float<T>(acc / l);
+  float value = acc / l;
+  if (gate != nullptr) {
+    // an output gate over the concatenated heads: value * sigmoid(g), written
+    // by a kernel further ahead in the chain (the products of this layer)
+    const float g = to_float(behind_wait(gate)[token * gate_stride + static_cast<long long>(head) * head_dim + d]);
+    value *= 1.0f / (1.0f + expf(-g));
+  }
+  out[(static_cast<size_t>(token) * heads + head) * head_dim + d] = from_float<T>(value);
 }
 
 }  // namespace mxb
@@ -993,6 +1000,11 @@ struct DecodeProject {
   long long ldw = 0;
   int hidden = 0, tokens = 0;
   float* summands = nullptr;         // [heads, tokens, hidden]
+  // An output gate (optional, with or without the projection): the heads'
+  // output times sigmoid(gate[token, head * head_dim + d]), rows gate_stride
+  // values apart, in the type of q.
+  const void* gate = nullptr;
+  long long gate_stride = 0;
 };
 
 template <typename T, int HD, int G>
@@ -1000,7 +1012,7 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
                          const int* block_tables, int max_pages, const int* row_token,
                          const int* row_request, const int* positions, int rows, int heads,
                          int kv_heads, int page_tokens, int num_pages, int max_splits, int window, int chunk,
-                         float scale, int* status, cudaStream_t stream) {
+                         float scale, int* status, cudaStream_t stream, DecodeProject project = DecodeProject()) {
   dim3 grid(max_splits, kv_heads, rows);
   constexpr int kElems = Vec16<T>::kElems;
   constexpr size_t kStage = 2 * static_cast<size_t>(kSplitKeys) * HD * sizeof(T);       // keys and values
@@ -1020,7 +1032,8 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
-                                         row_token, positions, rows, heads, HD, max_splits, window, chunk, 0, status));
+                                         row_token, positions, rows, heads, HD, max_splits, window, chunk, 0,
+                                         static_cast<const T*>(project.gate), project.gate_stride, status));
 }
 
 static int decode_resident_blocks = 444;   // blocks of the decode attention that fit the GPU at once (3 an SM); 0: always one block per tile
@@ -1037,12 +1050,14 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
     if (project.w != nullptr)
       return static_cast<int>(launch_merge_project<HD>(partial, project.w, project.ldw, project.summands, row_token,
                                                        positions, rows, project.tokens, heads, project.hidden,
-                                                       max_splits, window, chunk, slots, kSplitKeys, kDecodeMinusHuge, status,
-                                                       stream));
+                                                       max_splits, window, chunk, slots, kSplitKeys, kDecodeMinusHuge,
+                                                       static_cast<const __nv_bfloat16*>(project.gate),
+                                                       project.gate_stride, status, stream));
     return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                            dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
                                            static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
-                                           row_token, positions, rows, heads, HD, max_splits, window, chunk, slots, status));
+                                           row_token, positions, rows, heads, HD, max_splits, window, chunk, slots,
+                                           static_cast<const __nv_bfloat16*>(project.gate), project.gate_stride, status));
   };
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
@@ -1132,13 +1147,17 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
                                        const int* row_request, const int* positions, int rows,
                                        int heads, int kv_heads, int head_dim, int page_tokens,
                                        int num_pages, int max_splits, int window, int chunk, float scale,
-                                       int dtype, int* status, cudaStream_t stream) {
+                                       int dtype, const void* gate, long long gate_stride, int* status,
+                                       cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) || max_splits <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const int group = heads / kv_heads;
+  DecodeProject project;   // no projection here; the gate, if any
+  project.gate = gate;
+  project.gate_stride = gate_stride;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
-             heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream
+             heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
 #define BY_GROUP(T, HD)                                        \
   if (group == 1) return launch_decode<T, HD, 1>(ARGS);        \
   if (group == 2) return launch_decode<T, HD, 2>(ARGS);        \
@@ -1174,7 +1193,8 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
                                                const int* row_request, const int* positions, int rows, int tokens,
                                                int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                                int max_splits, int window, int chunk, float scale, const void* w, long long ldw,
-                                               int hidden, float* summands, int* status, cudaStream_t stream) {
+                                               int hidden, float* summands, const void* gate, long long gate_stride,
+                                               int* status, cudaStream_t stream) {
   if (rows <= 0 || hidden <= 0 || max_splits <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_paged_attention_decode_project_supported(head_dim, heads, kv_heads, kBF16, tokens, w, ldw))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -1184,6 +1204,8 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
   project.hidden = hidden;
   project.tokens = tokens;
   project.summands = summands;
+  project.gate = gate;
+  project.gate_stride = gate_stride;
   void* out = nullptr;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
@@ -1255,7 +1277,7 @@ MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache,
   if (e != cudaSuccess) return static_cast<int>(e);
   return mxb_paged_attention_decode(q, cache, out, scratch, block_tables, max_pages, row_token,
                                     row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
-                                    num_pages, splits, window, 0, scale, dtype, status, stream);
+                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, status, stream);
 }
 
 MXB_TIMELINE_EXPORT(mxb_timeline_attention)

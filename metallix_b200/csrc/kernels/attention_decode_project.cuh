@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(kProjectThreads)
 decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ w, long long ldw,
                             float* __restrict__ summands, const int* __restrict__ row_token,
                             const int* __restrict__ positions, int rows, int tokens, int heads, int hidden,
-                            int max_splits, int window, int chunk, int slots, int split_keys, float minus_huge, int* status) {
+                            int max_splits, int window, int chunk, int slots, int split_keys, float minus_huge,
+                            const __nv_bfloat16* __restrict__ gate, long long gate_stride, int* status) {
   constexpr int PITCH = HD * 2 + 16;  // bytes per row of a tile: rows a warp reads together fall on all banks
   constexpr int X_ROWS = MB * 8;
   extern __shared__ __align__(128) unsigned char project_shared[];
@@ -98,6 +99,14 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
     float2 acc[HD / 64];
 #pragma unroll
     for (int h = 0; h < HD / 64; ++h) acc[h] = make_float2(0.0f, 0.0f);
+    // The gate of this lane's two values per 64 (an output gate over the
+    // concatenated heads, optional): asked for now, used after the merge.
+    __nv_bfloat162 gates[HD / 64];
+    if (gate != nullptr) {
+      const __nv_bfloat16* g = behind_wait(gate) + token * gate_stride + head * HD + lane * 2;
+#pragma unroll
+      for (int h = 0; h < HD / 64; ++h) gates[h] = *reinterpret_cast<const __nv_bfloat162*>(g + h * 64);
+    }
     for (int chunk = 0; chunk < splits; chunk += kChunk) {
       const int live = min(kChunk, splits - chunk);
       float mine = minus_huge, mine_sum = 0.0f;
@@ -156,9 +165,16 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
       m = round_max;
     }
 #pragma unroll
-    for (int h = 0; h < HD / 64; ++h)
+    for (int h = 0; h < HD / 64; ++h) {
+      float2 value = make_float2(acc[h].x / l, acc[h].y / l);
+      if (gate != nullptr) {
+        const float2 g = __bfloat1622float2(gates[h]);
+        value.x *= 1.0f / (1.0f + expf(-g.x));
+        value.y *= 1.0f / (1.0f + expf(-g.y));
+      }
       *reinterpret_cast<__nv_bfloat162*>(s_x + token * PITCH + (h * 64 + lane * 2) * 2) =
-          __floats2bfloat162_rn(acc[h].x / l, acc[h].y / l);
+          __floats2bfloat162_rn(value.x, value.y);
+    }
   }
   __syncthreads();
   const bool landed = barrier_wait(&barrier, 0, status);
@@ -216,7 +232,8 @@ template <int HD>
 static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat16* w, long long ldw, float* summands,
                                         const int* row_token, const int* positions, int rows, int tokens, int heads,
                                         int hidden, int max_splits, int window, int chunk, int slots, int split_keys,
-                                        float minus_huge, int* status, cudaStream_t stream) {
+                                        float minus_huge, const __nv_bfloat16* gate, long long gate_stride, int* status,
+                                        cudaStream_t stream) {
   const dim3 grid((hidden + kProjectColumns - 1) / kProjectColumns, heads);
 #define GO(MB)                                                                                                       \
   {                                                                                                                  \
@@ -228,7 +245,7 @@ static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat1
     }                                                                                                                \
     return launch_chained(kernel, grid, dim3(kProjectThreads), shared, stream, partial, w, ldw, summands, row_token,  \
                           positions, rows, tokens, heads, hidden, max_splits, window, chunk, slots, split_keys, minus_huge,  \
-                          status);                                                                                   \
+                          gate, gate_stride, status);                                                                                   \
   }
   if (tokens <= 8) GO(1)
   if (tokens <= 16) GO(2)

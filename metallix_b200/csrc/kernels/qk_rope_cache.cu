@@ -269,8 +269,8 @@ qk_rownorm_rope_cache_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     int rotary_dim, int interleaved, int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
     float eps, int* status) {
-  extern __shared__ float rows[];   // the q row, then the k row
-  __shared__ float scratch[33];
+  extern __shared__ __align__(16) float rows[];   // the q row, then the k row
+  __shared__ float scratch[66];
   using Values = Pack<T, V>;
   chain_release();
   // Up to chain_wait(): the step's integers only.
@@ -329,31 +329,76 @@ qk_rownorm_rope_cache_kernel(
           *reinterpret_cast<const Values*>(v_src + i);
     }
   }
-  // block_sum's barriers also make the rows visible to every thread
-  q_sum = block_sum(q_sum, scratch);
-  k_sum = block_sum(k_sum, scratch);
+  // Both sums at once; the barriers also make the rows visible to every thread.
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    q_sum = warp_sum(q_sum);
+    k_sum = warp_sum(k_sum);
+    if (lane == 0) { scratch[warp] = q_sum; scratch[32 + warp] = k_sum; }
+    __syncthreads();
+    if (warp == 0) {
+      const float a = warp_sum(lane < warps ? scratch[lane] : 0.0f);
+      const float b = warp_sum(lane < warps ? scratch[32 + lane] : 0.0f);
+      if (lane == 0) { scratch[64] = a; scratch[65] = b; }
+    }
+    __syncthreads();
+    q_sum = scratch[64];
+    k_sum = scratch[65];
+  }
   const int half = rotary_dim >> 1;
 
   auto finish = [&](const float* row, int width, float sum, const float* weight, bool is_q) {
     const float scale = weight != nullptr ? rsqrtf(sum / static_cast<float>(width) + eps) : 1.0f;
     for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
       const int h = i / head_dim, d0 = i - h * head_dim;   // V divides head_dim: a vector stays in one head
+      float x[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[j] = row[i + j] * scale;
+      if (weight != nullptr) {
+        if (V % 4 == 0) {
+#pragma unroll
+          for (int j = 0; j < V; j += 4) {
+            const float4 g = *reinterpret_cast<const float4*>(weight + i + j);
+            x[j] *= g.x; x[j + 1] *= g.y; x[j + 2] *= g.z; x[j + 3] *= g.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) x[j] *= weight[i + j];
+        }
+      }
+      if (rotate && d0 < rotary_dim) {
+        if (interleaved && V >= 2) {
+          // both values of a pair sit in this vector
+#pragma unroll
+          for (int j = 0; j < V; j += 2) {
+            if (d0 + j < rotary_dim) {
+              const int pair = (d0 + j) >> 1;
+              const float c = cos_table[static_cast<size_t>(pos) * half + pair];
+              const float s = sin_table[static_cast<size_t>(pos) * half + pair];
+              const float a = x[j], b = x[j + 1];
+              x[j] = a * c - b * s;
+              x[j + 1] = b * c + a * s;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const int d = d0 + j;
+            if (d < rotary_dim) {
+              const bool first = interleaved ? (d & 1) == 0 : d < half;
+              const int pair = interleaved ? d >> 1 : (first ? d : d - half);
+              const int partner = i + j + (interleaved ? (first ? 1 : -1) : (first ? half : -half));
+              const float y = row[partner] * scale * (weight != nullptr ? weight[partner] : 1.0f);
+              const float c = cos_table[static_cast<size_t>(pos) * half + pair];
+              const float s = sin_table[static_cast<size_t>(pos) * half + pair];
+              x[j] = first ? x[j] * c - y * s : x[j] * c + y * s;
+            }
+          }
+        }
+      }
       Values out;
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const int d = d0 + j;
-        float x = row[i + j] * scale * (weight != nullptr ? weight[i + j] : 1.0f);
-        if (rotate && d < rotary_dim) {
-          const bool first = interleaved ? (d & 1) == 0 : d < half;
-          const int pair = interleaved ? d >> 1 : (first ? d : d - half);
-          const int partner = i + j + (interleaved ? (first ? 1 : -1) : (first ? half : -half));
-          const float y = row[partner] * scale * (weight != nullptr ? weight[partner] : 1.0f);
-          const float c = cos_table[static_cast<size_t>(pos) * half + pair];
-          const float s = sin_table[static_cast<size_t>(pos) * half + pair];
-          x = first ? x * c - y * s : x * c + y * s;
-        }
-        out.v[j] = from_float<T>(x);
-      }
+      for (int j = 0; j < V; ++j) out.v[j] = from_float<T>(x[j]);
       if (is_q) *reinterpret_cast<Values*>(q_out + static_cast<size_t>(t) * width + i) = out;
       else *reinterpret_cast<Values*>(key_page + h * head_stride + d0) = out;
     }
@@ -386,7 +431,8 @@ MXB_API int mxb_qk_norm_rope_cache(
     if (head_dim & 1) return static_cast<int>(cudaErrorInvalidValue);
     const int vector = 16 / element;
     const bool wide = head_dim % vector == 0 && aligned(q_in, q_stride) && aligned(k_in, k_stride) &&
-                      aligned(v_in, v_stride) && aligned(q_out, 0) && aligned(cache, 0);
+                      aligned(v_in, v_stride) && aligned(q_out, 0) && aligned(cache, 0) &&
+                      aligned(q_weight, 0) && aligned(k_weight, 0);
     const size_t shared = static_cast<size_t>(heads + kv_heads) * head_dim * sizeof(float);
     cudaError_t launch_status = cudaSuccess;
 #define ROW_LAUNCH(T, V) do { \

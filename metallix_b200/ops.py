@@ -38,14 +38,14 @@ _SIGNATURES = {
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _I, _P, _P],
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                   _F, _I, _P, _P],
+                                   _F, _I, _P, _L, _P, _P],
     "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
     "mxb_sigmoid_gate": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _P],
     "mxb_softcap": [_P, _F, _L, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_decode_project_supported": [_I, _I, _I, _I, _I, _P, _L],
     "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                           _F, _P, _L, _I, _P, _P, _P],
+                                           _F, _P, _L, _I, _P, _P, _L, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
     "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -617,13 +617,16 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
                            block_tables: torch.Tensor, row_token: torch.Tensor,
                            row_request: torch.Tensor, positions: torch.Tensor, scale: float,
                            longest_context: int, window: int = 0,
-                           partial: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
+                           partial: Optional[torch.Tensor] = None, chunk: int = 0,
+                           gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of single tokens over their requests' cached keys, split
     along the keys. ``row_token[i]`` is the token (row of q and out) of the
     i-th decoded request, negative for a padding row; ``row_request[i]`` its
     row of ``block_tables``. ``longest_context`` bounds positions + 1 and
     fixes the number of splits. ``partial`` is float32 scratch of
-    rows * heads * splits * (head_dim + 2) values, allocated here if absent."""
+    rows * heads * splits * (head_dim + 2) values, allocated here if absent.
+    ``gate`` ([tokens, heads * head_dim] in q's type, rows may be strided):
+    the output is multiplied by sigmoid(gate) as it is written."""
     dtype = q.dtype
     _check(q, "q", tuple(_CODES), 3)
     _check(out, "out", (dtype,), 3)
@@ -645,11 +648,24 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
         partial = torch.empty(need, dtype=torch.float32, device=q.device)
     _check(partial, "partial", (torch.float32,))
     _need(partial.numel() >= need, f"partial holds {partial.numel()} values, {need} are needed")
+    gate_stride = _gate_stride(gate, q)
     _call("mxb_paged_attention_decode", q.data_ptr(), cache.data_ptr(), out.data_ptr(), partial.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
-          int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], status_word(q.device).data_ptr(), _stream())
+          int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], _ptr(gate), gate_stride,
+          status_word(q.device).data_ptr(), _stream())
     return out
+
+
+def _gate_stride(gate: Optional[torch.Tensor], q: torch.Tensor) -> int:
+    """Checks an output gate against q [tokens, heads, head_dim]; its row stride."""
+    if gate is None:
+        return 0
+    tokens, heads, head_dim = q.shape
+    _need(gate.is_cuda and gate.dtype == q.dtype and gate.dim() == 2 and gate.stride(1) == 1
+          and gate.shape == (tokens, heads * head_dim), "gate must be [tokens, heads * head_dim] in q's type")
+    _need(gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0, "gate rows must start on 4-byte boundaries")
+    return gate.stride(0)
 
 
 def decode_project_supported(head_dim: int, heads: int, kv_heads: int, dtype: torch.dtype, tokens: int,
@@ -664,11 +680,13 @@ def decode_project_supported(head_dim: int, heads: int, kv_heads: int, dtype: to
 def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                                    row_token: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor,
                                    scale: float, longest_context: int, weight: torch.Tensor,
-                                   window: int = 0, chunk: int = 0) -> torch.Tensor:
+                                   window: int = 0, chunk: int = 0,
+                                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``paged_attention_decode`` followed at once by the output projection
     ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 64 tokens in
     bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
-    over k left in one summand per head, for ``add_rmsnorm`` to add up."""
+    over k left in one summand per head, for ``add_rmsnorm`` to add up. With
+    ``gate`` the heads' output is multiplied by sigmoid(gate) ahead of the projection."""
     _check(q, "q", (torch.bfloat16,), 3)
     _check(cache, "cache", (torch.bfloat16,), 5)
     tokens, heads, head_dim = q.shape
@@ -686,10 +704,12 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
     partial = torch.empty(rows * heads * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
     hidden = weight.shape[0]
     summands = torch.empty((heads, tokens, hidden), dtype=torch.float32, device=q.device)
+    gate_stride = _gate_stride(gate, q)
     _call("mxb_paged_attention_decode_project", q.data_ptr(), cache.data_ptr(), partial.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, tokens, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), int(chunk or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
+          _ptr(gate), gate_stride,
           status_word(q.device).data_ptr(), _stream())
     return summands
 

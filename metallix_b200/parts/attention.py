@@ -239,21 +239,25 @@ class GQAttention:
         tiles = self._tiles(ctx)
         multi_tiles = tiles["multi_tiles"]
         split = tiles["decode_rows"] and self.split_decode
+        # A step of single tokens only: the gate rides in the kernel that puts the
+        # splits together; any other step gates all tokens at once below.
+        gate_in_merge = gate is not None and bool(split) and multi_tiles == 0
         if (summands and split and multi_tiles == 0 and tokens <= PROJECT_TOKENS and self.o.rows_are_short()
-                and not self.gated
                 and ops.decode_project_supported(self.head_dim, self.num_heads, self.num_kv_heads, self.dtype,
                                                  tokens, self.o.weight)):
             # Only single tokens, at most 64 of them: the splits are merged
             # and projected by one kernel, one summand per head.
             return ops.paged_attention_decode_project(
                 q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
-                ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window, self.chunk)
+                ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window, self.chunk,
+                gate=gate)
         out = torch.empty_like(q_heads)
         if split:
             # Requests that bring one token: split along the keys.
             ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],
                                        tiles["decode_request"], ctx.positions, self.scale,
-                                       tiles["longest_context"], self.window, chunk=self.chunk)
+                                       tiles["longest_context"], self.window, chunk=self.chunk,
+                                       gate=gate if gate_in_merge else None)
         if self.flash:
             # Requests that bring several tokens: tensor cores, tiles of 128.
             if tiles["wide_request"].numel():
@@ -268,7 +272,7 @@ class GQAttention:
                                      tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
                                      self.scale, self.window, self.chunk)
         heads_out = out.view(tokens, self.q_size)
-        if gate is not None:
+        if gate is not None and not gate_in_merge:
             ops.sigmoid_gate(heads_out, gate, out=heads_out)
         return self.o.forward(heads_out)
 

@@ -147,7 +147,7 @@ def test_rotation_keeps_accuracy_at_far_positions(ops):
 
 
 # ------------------------------------------------------------------ attention
-def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, shuffle_seed=0):
+def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, shuffle_seed=0, chunk=0):
     """Several requests; request r's last ``lengths[r][1]`` positions are the
     queries, all ``lengths[r][0]`` positions sit in a cache whose pages are
     handed out in shuffled order."""
@@ -181,7 +181,7 @@ def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, sh
     out = torch.empty_like(q_all)
     ops.paged_attention_tile(q_all, cache, out, dev(tables, torch.int32), dev(tile_request, torch.int32),
                              dev(tile_start, torch.int32), dev(tile_length, torch.int32),
-                             dev(positions, torch.int32), scale, window)
+                             dev(positions, torch.int32), scale, window, chunk)
     ops.check_status("cuda")
     return out.cpu().double().numpy()
 
@@ -261,6 +261,157 @@ def test_window_edge(ops, dtype):
         assert near == seen, (target, seen)
 
 
+# ------------------------------------------------------ a mask of chunks
+# A query sees the keys of its own chunk of `chunk` positions (counted from
+# position 0) up to itself. The plain side is tests/plain_mekazen.py.
+def chunk_reference(q, k, v, scale, chunk, last=None):
+    """The plain attention of all rows, or of the ``last`` rows only."""
+    import plain_mekazen
+    total = q.shape[0]
+    rows = None if last is None else range(total - last, total)
+    return plain_mekazen.masked_attention(q, k, v, list(range(total)), scale, chunk, rows=rows)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk", [1, 7, 16, 50])
+def test_paged_attention_chunks(ops, dtype, chunk):
+    """Prompt portions and single tokens, chunk sizes below, at and across the
+    page size (8) and the key tile (32), and a window on top of the chunks."""
+    rng = np.random.default_rng(chunk)
+    heads, kv_heads, head_dim = 4, 2, 32
+    lengths = [(110, 110), (77, 1), (101, 1), (50, 9)]
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n, _ in lengths]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    out = run_attention(ops, dtype, q, k, v, lengths, 8, 0.25, chunk=chunk)
+    cursor = 0
+    for r, (total, queries) in enumerate(lengths):
+        ref = chunk_reference(q[r], k[r], v[r], 0.25, chunk, last=queries)
+        assert np.abs(out[cursor:cursor + queries] - ref).max() < tol(dtype, 5e-6, 2e-2), r
+        cursor += queries
+    # both rules at once: the later of the two first keys counts
+    both = run_attention(ops, dtype, q[:1], k[:1], v[:1], lengths[:1], 8, 0.25, window=5, chunk=chunk)
+    position = np.arange(110)
+    for t in (0, 4, 49, 50, 51, 109):
+        first = max(t - 4, t - t % chunk)
+        for head in range(heads):
+            scores = (k[0][first:t + 1, head // 2] @ q[0][t, head]) * 0.25
+            weights = np.exp(scores - scores.max())
+            want = (weights / weights.sum()) @ v[0][first:t + 1, head // 2]
+            assert np.abs(both[t, head] - want).max() < tol(dtype, 5e-6, 2e-2), (t, head)
+
+
+def strong_key_case(rng, dtype, total, heads, kv_heads, head_dim, target, query, axis=3):
+    """Small random q, k; the key at ``target`` and the query at ``query`` point
+    the same way so strongly that, if seen, the output is that key's value."""
+    k = rounded(rng.normal(size=(total, kv_heads, head_dim)) * 0.1, dtype)
+    v = rounded(rng.normal(size=(total, kv_heads, head_dim)), dtype)
+    q = rounded(rng.normal(size=(total, heads, head_dim)) * 0.1, dtype)
+    k[target, :, :] = 0.0
+    k[target, :, axis] = 16.0
+    q[query, :, axis] = 16.0
+    return q, k, v
+
+
+# (chunk, page): chunks of whole pages, chunks that end inside a page, a chunk larger than a key tile
+CHUNK_EDGES = [(48, 16), (50, 16), (200, 8), (130, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk, page", CHUNK_EDGES)
+def test_chunk_edges_general_kernel(ops, dtype, chunk, page):
+    """The strong key at the first position of the query's chunk is seen, the
+    one just ahead of the chunk is not; for the chunk's first, second and last
+    query, as the last token of a portion and alone."""
+    heads, kv_heads, head_dim = 2, 1, 32
+    rng = np.random.default_rng(chunk)
+    start = 2 * chunk
+    for query in (start, start + 1, start + chunk - 1):
+        for target, seen in ((start, True), (start - 1, False), (0, False), (query, True)):
+            total = query + 1
+            q, k, v = strong_key_case(rng, dtype, total, heads, kv_heads, head_dim, target, query)
+            for queries in (1, min(40, total)):
+                out = run_attention(ops, dtype, [q], [k], [v], [(total, queries)], page, head_dim ** -0.5,
+                                    chunk=chunk, shuffle_seed=query)
+                near = np.abs(out[-1] - v[target, 0]).max() < 1e-2
+                assert near == seen, (query, target, queries)
+                ref = chunk_reference(q, k, v, head_dim ** -0.5, chunk, last=queries)
+                assert np.abs(out - ref).max() < tol(dtype, 1e-5, 2e-2), (query, target, queries)
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+@pytest.mark.parametrize("chunk, page", CHUNK_EDGES)
+def test_chunk_edges_prompt_kernels(ops, kernel, chunk, page):
+    """The same edges through the tensor-core prompt kernels: a portion of 70
+    tokens that crosses a chunk's edge, every row against the plain side, and
+    the strong key just inside and just outside."""
+    heads, kv_heads, head_dim, dtype = 4, 2, 64, torch.bfloat16
+    rng = np.random.default_rng(chunk + 1)
+    start = 2 * chunk
+    for query in (start, start + 1, start + chunk - 1):
+        for target, seen in ((start, True), (start - 1, False), (query, True)):
+            total = query + 1
+            q, k, v = strong_key_case(rng, dtype, total, heads, kv_heads, head_dim, target, query, axis=5)
+            out = run_flash(ops, [q], [k], [v], [(total, min(70, total))], page, head_dim ** -0.5, seed=query,
+                            kernel=kernel, chunk=chunk)
+            for head in range(heads):
+                near = np.abs(out[-1, head] - v[target, head // 2]).max() < 1e-2
+                assert near == seen, (query, target, head)
+            ref = chunk_reference(q, k, v, head_dim ** -0.5, chunk, last=min(70, total))
+            assert np.abs(out - ref).max() < 2e-2, (query, target)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk, page", CHUNK_EDGES + [(1000, 16)])
+def test_chunk_edges_split_key_decode(ops, dtype, chunk, page):
+    """... and through the split-key decode kernels (one block per tile and
+    blocks that walk over tiles), alone and with the merge that also projects."""
+    heads, kv_heads, head_dim = 4, 2, 64
+    rng = np.random.default_rng(chunk + 2)
+    start = 2 * chunk
+    try:
+        for resident in (444, 0):
+            ops.set_decode_resident_blocks(resident)
+            for query in (start, start + 1, start + chunk - 1):
+                for target, seen in ((start, True), (start - 1, False), (query, True)):
+                    total = query + 1
+                    q, k, v = strong_key_case(rng, dtype, total, heads, kv_heads, head_dim, target, query, axis=9)
+                    out = run_decode_attention(ops, dtype, [q], [k], [v], [total], page, head_dim ** -0.5,
+                                               seed=query, chunk=chunk)
+                    ref = chunk_reference(q, k, v, head_dim ** -0.5, chunk, last=1)
+                    assert np.abs(out[0] - ref[0]).max() < tol(dtype, 1e-5, 2e-2), (query, target)
+                    for head in range(heads):
+                        near = np.abs(out[0, head] - v[target, head // 2]).max() < 1e-2
+                        assert near == seen, (resident, query, target, head)
+    finally:
+        ops.set_decode_resident_blocks(444)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_merge_with_an_output_gate(ops, dtype):
+    """out * sigmoid(gate) inside the kernel that puts the splits together, and
+    inside the one that also projects; the gate is a column range of a wider tensor."""
+    heads, kv_heads, head_dim, hidden = 4, 2, 64, 200
+    rng = np.random.default_rng(77)
+    totals = [300, 1, 129, 2049]
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n in totals]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    wide = rounded(rng.normal(size=(len(totals), 3 * heads * head_dim)) * 2.0, dtype)
+    gate = dev(wide, dtype)[:, heads * head_dim:2 * heads * head_dim]
+    plain_gate = 1.0 / (1.0 + np.exp(-wide[:, heads * head_dim:2 * heads * head_dim]))
+    plain_gate = plain_gate.reshape(len(totals), heads, head_dim)
+    bare = run_decode_attention(ops, dtype, q, k, v, totals, 16, 0.125, chunk=700)
+    gated = run_decode_attention(ops, dtype, q, k, v, totals, 16, 0.125, chunk=700, gate=gate)
+    assert np.abs(gated - bare * plain_gate).max() < tol(dtype, 1e-6, 1.5e-2)
+    if dtype == torch.bfloat16:
+        weight = rounded(rng.normal(size=(hidden, heads * head_dim)), dtype)
+        summands = run_decode_attention(ops, dtype, q, k, v, totals, 16, 0.125, chunk=700, gate=gate,
+                                        project=dev(weight, dtype))
+        want = (bare * plain_gate).reshape(len(totals), -1) @ weight.T
+        assert np.abs(summands.sum(axis=0) - want).max() < 2e-2 * np.abs(want).max()
+
+
 def test_attention_does_not_depend_on_the_cut(ops):
     """float32: the same query gives the same bits alone, in a tile of 16 and
     beside other requests."""
@@ -278,7 +429,7 @@ def test_attention_does_not_depend_on_the_cut(ops):
     assert np.array_equal(part[37:], whole[total - 12:total - 9])
 
 
-def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kernel="mma", tile=128):
+def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kernel="mma", tile=128, chunk=0):
     """A tensor-core prompt kernel ("mma": warp-level, "tcgen05": TMA and
     tensor memory) on requests whose last ``queries`` positions are the
     queries (bfloat16), cut into tiles of up to ``tile`` tokens."""
@@ -308,7 +459,7 @@ def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kerne
     ops.flash_prefill(q_all, dev(host_cache, dtype), out, dev(tables, torch.int32),
                       dev([t[0] for t in tiles], torch.int32), dev([t[1] for t in tiles], torch.int32),
                       dev([t[2] for t in tiles], torch.int32), dev(positions, torch.int32), scale, window,
-                      kernel=kernel)
+                      kernel=kernel, chunk=chunk)
     ops.check_status("cuda")
     return out.cpu().double().numpy()
 
@@ -402,7 +553,7 @@ def test_flash_prefill_with_a_tile_s_keys_shared_out(ops, shares):
 
 
 def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window=0, pad_rows=0, seed=0,
-                         project=None):
+                         project=None, chunk=0, gate=None):
     """One query (the last position) per request through the split-key kernel;
     with ``project`` (a weight on the device) through the kernel that also
     projects: the summands [heads, tokens, hidden] then."""
@@ -427,12 +578,13 @@ def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window
         summands = ops.paged_attention_decode_project(
             q_all, dev(host_cache, dtype), dev(tables, torch.int32), dev(rows, torch.int32),
             dev([max(r, 0) for r in rows], torch.int32), dev([t - 1 for t in totals], torch.int32), scale,
-            max(totals) + 300, project, window)
+            max(totals) + 300, project, window, chunk, gate=gate)
         ops.check_status("cuda")
         return summands.cpu().double().numpy()
     ops.paged_attention_decode(q_all, dev(host_cache, dtype), out, dev(tables, torch.int32),
                                dev(rows, torch.int32), dev([max(r, 0) for r in rows], torch.int32),
-                               dev([t - 1 for t in totals], torch.int32), scale, max(totals) + 300, window)
+                               dev([t - 1 for t in totals], torch.int32), scale, max(totals) + 300, window,
+                               chunk=chunk, gate=gate)
     ops.check_status("cuda")
     return out.cpu().double().numpy()
 
