@@ -73,7 +73,8 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                      const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                      const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
-                     int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, int* status) {
+                     int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale,
+                     const __nv_bfloat16* __restrict__ gate, long long gate_stride, int* status) {
   constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
   constexpr int TILE_BYTES = kFlashKeys * HD * 2;
   extern __shared__ __align__(128) unsigned char shared[];
@@ -265,11 +266,22 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   const float inv_lo = valid_lo ? 1.0f / l_lo : 0.0f, inv_hi = valid_hi ? 1.0f / l_hi : 0.0f;
   __nv_bfloat16* out_lo = out + (static_cast<size_t>(t0 + row_lo) * heads + head) * HD;
   __nv_bfloat16* out_hi = out + (static_cast<size_t>(t0 + row_hi) * heads + head) * HD;
+  const __nv_bfloat16* gate_lo = gate != nullptr ? gate + (t0 + row_lo) * gate_stride + head * HD : nullptr;
+  const __nv_bfloat16* gate_hi = gate != nullptr ? gate + (t0 + row_hi) * gate_stride + head * HD : nullptr;
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) {
     const int d = i * 8 + 2 * t;
-    if (valid_lo) *reinterpret_cast<uint32_t*>(out_lo + d) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
-    if (valid_hi) *reinterpret_cast<uint32_t*>(out_hi + d) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+    float2 g_lo = make_float2(1.0f, 1.0f), g_hi = g_lo;
+    if (gate != nullptr && valid_lo) {
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate_lo + d));
+      g_lo = make_float2(sigmoid_of(g.x), sigmoid_of(g.y));
+    }
+    if (gate != nullptr && valid_hi) {
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate_hi + d));
+      g_hi = make_float2(sigmoid_of(g.x), sigmoid_of(g.y));
+    }
+    if (valid_lo) *reinterpret_cast<uint32_t*>(out_lo + d) = pack_bf16(o[i][0] * inv_lo * g_lo.x, o[i][1] * inv_lo * g_lo.y);
+    if (valid_hi) *reinterpret_cast<uint32_t*>(out_hi + d) = pack_bf16(o[i][2] * inv_hi * g_hi.x, o[i][3] * inv_hi * g_hi.y);
   }
 }
 
@@ -277,7 +289,8 @@ template <int HD>
 static int launch_flash(const void* q, const void* cache, void* out, const int* block_tables, int max_pages,
                         const int* tile_request, const int* tile_start, const int* tile_length,
                         const int* positions, int tiles, int heads, int kv_heads, int page_tokens,
-                        int num_pages, int window, int chunk, float scale, int* status, cudaStream_t stream) {
+                        int num_pages, int window, int chunk, float scale, const void* gate, long long gate_stride,
+                        int* status, cudaStream_t stream) {
   const int shared = 4 * kFlashKeys * HD * 2;
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
@@ -286,7 +299,8 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
   kernel<<<grid, kFlashThreads, shared, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,
-      positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, status);
+      positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
+      static_cast<const __nv_bfloat16*>(gate), gate_stride, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -308,12 +322,15 @@ MXB_API int mxb_flash_prefill(const void* q, const void* cache, void* out, const
                               int max_pages, const int* tile_request, const int* tile_start,
                               const int* tile_length, const int* positions, int tiles, int heads,
                               int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
-                              float scale, int dtype, int* status, cudaStream_t stream) {
+                              float scale, int dtype, const void* gate, long long gate_stride, int* status,
+                              cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (!mxb_flash_prefill_supported(head_dim, heads, kv_heads, dtype)) return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, status, stream);
+                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, status,
+                            stream);
   return launch_flash<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, status, stream);
+                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, status,
+                            stream);
 }

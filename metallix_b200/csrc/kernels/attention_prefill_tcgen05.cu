@@ -76,7 +76,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                              const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
                              int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale,
-                             int shared_bytes, float* __restrict__ partial, int* status) {
+                             int shared_bytes, float* __restrict__ partial, const __nv_bfloat16* __restrict__ gate,
+                             long long gate_stride, int* status) {
   using Config = FaConfig<HD>;
   constexpr int MAX_STAGES = Config::kKeyStages;
   constexpr int HALVES = Config::kHalves;
@@ -392,6 +393,19 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     } else if (ok && valid) {
       const float inv = 1.0f / l;
       __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + row) * heads + head) * HD + part * PART_HD;
+      if (gate != nullptr) {   // an output gate over the concatenated heads: acc * sigmoid(gate) / l
+        const __nv_bfloat16* g = gate + (t0 + row) * gate_stride + head * HD + part * PART_HD;
+#pragma unroll
+        for (int c = 0; c < PART_HD; c += 8) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(g + c);
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[c + 2 * j] *= sigmoid_of(__uint_as_float(words[j] << 16));
+            acc[c + 2 * j + 1] *= sigmoid_of(__uint_as_float(words[j] & 0xffff0000u));
+          }
+        }
+      }
 #pragma unroll
       for (int c = 0; c < PART_HD; c += 8) {
         *reinterpret_cast<uint4*>(dst + c) =
@@ -425,7 +439,7 @@ template <int HD>
 __global__ void __launch_bounds__(HD)
 flash_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                            const int* __restrict__ tile_start, const int* __restrict__ tile_length, int heads,
-                           int shares) {
+                           int shares, const __nv_bfloat16* __restrict__ gate, long long gate_stride) {
   const int head = blockIdx.x, tile = blockIdx.y, d = threadIdx.x;
   const int t0 = tile_start[tile], n = tile_length[tile];
   for (int row = blockIdx.z; row < n; row += kMergeGroups) {
@@ -448,6 +462,7 @@ flash_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __r
       value = fmaf(weight, values[s], value);
       sum = fmaf(weight, sums[s], sum);
     }
+    if (gate != nullptr) value *= sigmoid_of(__bfloat162float(gate[(t0 + row) * gate_stride + head * HD + d]));
     out[(static_cast<size_t>(t0 + row) * heads + head) * HD + d] = __float2bfloat16_rn(value / sum);
   }
 }
@@ -456,8 +471,8 @@ template <int HD>
 static int launch_flash_tc(const void* q, const void* cache, void* out, const int* block_tables, int max_pages,
                            const int* tile_request, const int* tile_start, const int* tile_length,
                            const int* positions, int tokens, int tiles, int heads, int kv_heads, int page_tokens,
-                           int num_pages, int window, int chunk, float scale, int key_shares, float* partial, int* status,
-                           cudaStream_t stream) {
+                           int num_pages, int window, int chunk, float scale, int key_shares, float* partial,
+                           const void* gate, long long gate_stride, int* status, cudaStream_t stream) {
   using Config = FaConfig<HD>;
   CUtensorMap map_q, map_cache;
   // q as [tokens, heads * HD]; the cache as [pages * 2 * kv_heads * page_tokens, HD].
@@ -481,11 +496,12 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
   kernel<<<grid, kFaThreads, shared_bytes, stream>>>(
       map_q, map_cache, static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start,
       tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, shared_bytes,
-      shared_out ? partial : nullptr, status);
+      shared_out ? partial : nullptr, static_cast<const __nv_bfloat16*>(gate), gate_stride, status);
   e = cudaGetLastError();
   if (e != cudaSuccess || !shared_out) return static_cast<int>(e);
   flash_prefill_merge_kernel<HD><<<dim3(heads, tiles, kMergeGroups), HD, 0, stream>>>(
-      partial, static_cast<__nv_bfloat16*>(out), tile_start, tile_length, heads, key_shares);
+      partial, static_cast<__nv_bfloat16*>(out), tile_start, tile_length, heads, key_shares,
+      static_cast<const __nv_bfloat16*>(gate), gate_stride);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -512,20 +528,20 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
                                       const int* tile_length, const int* positions, int tokens, int tiles,
                                       int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                       int window, int chunk, float scale, int dtype, int key_shares, float* partial,
-                                      int* status, cudaStream_t stream) {
+                                      const void* gate, long long gate_stride, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (key_shares < 1 || key_shares > kMergeShares || (key_shares > 1 && partial == nullptr))
     return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page_tokens, dtype))
     return static_cast<int>(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
-      (reinterpret_cast<uintptr_t>(out) & 15))
+      (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(gate) & 15) || ((gate_stride * 2) & 15))
     return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash_tc<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                                positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
-                               key_shares, partial, status, stream);
+                               key_shares, partial, gate, gate_stride, status, stream);
   return launch_flash_tc<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                               positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
-                              key_shares, partial, status, stream);
+                              key_shares, partial, gate, gate_stride, status, stream);
 }

@@ -30,7 +30,8 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
                             const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                             const int* __restrict__ tile_length, const int* __restrict__ positions,
                             int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
-                            int window, int chunk, float scale, int* status) {
+                            int window, int chunk, float scale, const T* __restrict__ gate, long long gate_stride,
+                            int* status) {
   extern __shared__ float shared[];
   float* sQ = shared;                                   // [16][head_dim]
   float* sK = sQ + kTileQueries * head_dim;             // [32][head_dim + 1]
@@ -133,10 +134,11 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
   if (row_valid) {
     const float inv = 1.0f / l;
     T* dst = out + (static_cast<size_t>(t0 + r) * heads + head) * head_dim;
+    const T* g = gate != nullptr ? gate + (t0 + r) * gate_stride + static_cast<long long>(head) * head_dim : nullptr;
 #pragma unroll
     for (int j = 0; j < DPT; ++j) {
       const int d = lane8 + 8 * j;
-      if (d < head_dim) dst[d] = from_float<T>(acc[j] * inv);
+      if (d < head_dim) dst[d] = from_float<T>(acc[j] * inv * (g != nullptr ? sigmoid_of(to_float(g[d])) : 1.0f));
     }
   }
 }
@@ -146,7 +148,7 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
                        int max_pages, const int* tile_request, const int* tile_start,
                        const int* tile_length, const int* positions, int tiles, int heads,
                        int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
-                       float scale, int* status, cudaStream_t stream) {
+                       float scale, const void* gate, long long gate_stride, int* status, cudaStream_t stream) {
   const size_t shared = sizeof(float) * (static_cast<size_t>(kTileQueries) * head_dim +
                                          static_cast<size_t>(kTileKeys) * (head_dim + 1) +
                                          static_cast<size_t>(kTileKeys) * head_dim +
@@ -160,7 +162,7 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
   kernel<<<grid, kTileThreads, shared, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(cache), static_cast<T*>(out), block_tables,
       max_pages, tile_request, tile_start, tile_length, positions, heads, kv_heads, head_dim,
-      page_tokens, num_pages, window, chunk, scale, status);
+      page_tokens, num_pages, window, chunk, scale, static_cast<const T*>(gate), gate_stride, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -176,12 +178,12 @@ MXB_API int mxb_paged_attention_tile(const void* q, const void* cache, void* out
                                      const int* tile_request, const int* tile_start,
                                      const int* tile_length, const int* positions, int tiles,
                                      int heads, int kv_heads, int head_dim, int page_tokens,
-                                     int num_pages, int window, int chunk, float scale, int dtype, int* status,
-                                     cudaStream_t stream) {
+                                     int num_pages, int window, int chunk, float scale, int dtype, const void* gate,
+                                     long long gate_stride, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (head_dim <= 0 || head_dim > 256 || heads % kv_heads != 0) return static_cast<int>(cudaErrorInvalidValue);
 #define ARGS q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length, positions, \
-             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, status, stream
+             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, status, stream
 #define DISPATCH(T)                                           \
   if (head_dim <= 16) return launch_tile<T, 2>(ARGS);         \
   if (head_dim <= 32) return launch_tile<T, 4>(ARGS);         \

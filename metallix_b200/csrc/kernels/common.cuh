@@ -61,6 +61,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// An output gate over the concatenated heads (optional in every attention
+// kernel): the value a kernel is about to write for (token, head, d) times
+// sigmoid(gate[token * gate_stride + head * head_dim + d]), in float32.
+__device__ __forceinline__ float sigmoid_of(float g) { return 1.0f / (1.0f + expf(-g)); }
+
 // The first key a query at position `pos` sees. Two rules, either or both:
 // a sliding window keeps the last `window` positions (keys > pos - window), a
 // chunked mask keeps the keys of the query's own chunk of `chunk` positions,

@@ -36,7 +36,7 @@ _SIGNATURES = {
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
                                _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                 _F, _I, _P, _P],
+                                 _F, _I, _P, _L, _P, _P],
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                                    _F, _I, _P, _L, _P, _P],
     "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
@@ -48,11 +48,11 @@ _SIGNATURES = {
                                            _F, _P, _L, _I, _P, _P, _L, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
-    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _L, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
     "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
-                                  _P, _P],
+                                  _P, _L, _P, _P],
     "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
     "mxb_flash_prefill_tcgen05_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
@@ -465,11 +465,14 @@ def write_cache(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slots: to
 def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor,
                          block_tables: torch.Tensor, tile_request: torch.Tensor,
                          tile_start: torch.Tensor, tile_length: torch.Tensor,
-                         positions: torch.Tensor, scale: float, window: int = 0, chunk: int = 0) -> torch.Tensor:
+                         positions: torch.Tensor, scale: float, window: int = 0, chunk: int = 0,
+                         gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of every query token over its request's cached keys (itself
     included) in float32; q and out are [tokens, heads, head_dim]. ``window``:
     only the last that many positions are seen; ``chunk``: only the keys of the
-    query's own chunk of that many positions, counted from position 0."""
+    query's own chunk of that many positions, counted from position 0;
+    ``gate`` ([tokens, heads * head_dim], rows may be strided): the output is
+    multiplied by sigmoid(gate) as it is written."""
     dtype = q.dtype
     _check(q, "q", tuple(_CODES), 3)
     _check(out, "out", (dtype,), 3)
@@ -491,7 +494,7 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
           block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(),
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
           kv_heads, head_dim, page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[dtype],
-          status_word(q.device).data_ptr(), _stream())
+          _ptr(gate), _gate_stride(gate, q), status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -539,7 +542,7 @@ def flash_key_shares(blocks: int, longest_context: int, window: int = 0, chunk: 
 def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
                   positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto",
-                  longest_context: int = 0, chunk: int = 0) -> torch.Tensor:
+                  longest_context: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
     float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
     of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
@@ -566,7 +569,10 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     if kernel == "auto":
         kernel = PROMPT_KERNEL
     _need(kernel in ("auto", "tcgen05", "mma"), f"unknown prompt-attention kernel {kernel!r}")
+    gate_stride = _gate_stride(gate, q)
     tcgen05 = flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page_tokens, q.dtype)
+    if gate is not None and (gate.data_ptr() % 16 or (gate_stride * 2) % 16):
+        tcgen05 = False   # its epilogue reads the gate 16 bytes at a time
     _need(tcgen05 or kernel != "tcgen05",
           f"the tcgen05 prompt kernel does not take head_dim {head_dim} with pages of {page_tokens} tokens")
     if tcgen05 and kernel != "mma":
@@ -579,7 +585,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
               block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
               tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
               page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
-              status_word(q.device).data_ptr(), _stream())
+              _ptr(gate), gate_stride, status_word(q.device).data_ptr(), _stream())
         if shares > 1:
             global _launches
             _launches += 1   # the kernel that puts the shares together
@@ -587,7 +593,8 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     _call("mxb_flash_prefill", q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
           positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,
-          int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], status_word(q.device).data_ptr(), _stream())
+          int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], _ptr(gate), gate_stride,
+          status_word(q.device).data_ptr(), _stream())
     return out
 
 

@@ -239,9 +239,7 @@ class GQAttention:
         tiles = self._tiles(ctx)
         multi_tiles = tiles["multi_tiles"]
         split = tiles["decode_rows"] and self.split_decode
-        # A step of single tokens only: the gate rides in the kernel that puts the
-        # splits together; any other step gates all tokens at once below.
-        gate_in_merge = gate is not None and bool(split) and multi_tiles == 0
+        # The gate, if any, rides in whichever kernel writes a token's output.
         if (summands and split and multi_tiles == 0 and tokens <= PROJECT_TOKENS and self.o.rows_are_short()
                 and ops.decode_project_supported(self.head_dim, self.num_heads, self.num_kv_heads, self.dtype,
                                                  tokens, self.o.weight)):
@@ -257,24 +255,21 @@ class GQAttention:
             ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],
                                        tiles["decode_request"], ctx.positions, self.scale,
                                        tiles["longest_context"], self.window, chunk=self.chunk,
-                                       gate=gate if gate_in_merge else None)
+                                       gate=gate)
         if self.flash:
             # Requests that bring several tokens: tensor cores, tiles of 128.
             if tiles["wide_request"].numel():
                 ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, tiles["wide_request"],
                                   tiles["wide_start"], tiles["wide_length"], ctx.positions, self.scale,
-                                  self.window, longest_context=tiles["longest_keys"], chunk=self.chunk)
+                                  self.window, longest_context=tiles["longest_keys"], chunk=self.chunk, gate=gate)
             rest = None if split else slice(multi_tiles, None)   # single tokens not yet served
         else:
             rest = slice(0, multi_tiles) if split else slice(0, None)
         if rest is not None and tiles["tile_request"][rest].numel():
             ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, tiles["tile_request"][rest],
                                      tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
-                                     self.scale, self.window, self.chunk)
-        heads_out = out.view(tokens, self.q_size)
-        if gate is not None and not gate_in_merge:
-            ops.sigmoid_gate(heads_out, gate, out=heads_out)
-        return self.o.forward(heads_out)
+                                     self.scale, self.window, self.chunk, gate=gate)
+        return self.o.forward(out.view(tokens, self.q_size))
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()

@@ -147,7 +147,7 @@ def test_rotation_keeps_accuracy_at_far_positions(ops):
 
 
 # ------------------------------------------------------------------ attention
-def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, shuffle_seed=0, chunk=0):
+def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, shuffle_seed=0, chunk=0, gate=None):
     """Several requests; request r's last ``lengths[r][1]`` positions are the
     queries, all ``lengths[r][0]`` positions sit in a cache whose pages are
     handed out in shuffled order."""
@@ -181,7 +181,7 @@ def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, sh
     out = torch.empty_like(q_all)
     ops.paged_attention_tile(q_all, cache, out, dev(tables, torch.int32), dev(tile_request, torch.int32),
                              dev(tile_start, torch.int32), dev(tile_length, torch.int32),
-                             dev(positions, torch.int32), scale, window, chunk)
+                             dev(positions, torch.int32), scale, window, chunk, gate=gate)
     ops.check_status("cuda")
     return out.cpu().double().numpy()
 
@@ -412,6 +412,35 @@ def test_decode_merge_with_an_output_gate(ops, dtype):
         assert np.abs(summands.sum(axis=0) - want).max() < 2e-2 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("path", ["general float32", "general bfloat16", "mma", "tcgen05", "tcgen05 shared keys"])
+def test_prompt_kernels_with_an_output_gate(ops, path):
+    """out * sigmoid(gate) as each prompt kernel writes its output, the gate a
+    column range of a wider tensor; a portion behind cached keys beside a whole prompt."""
+    dtype = torch.float32 if path == "general float32" else torch.bfloat16
+    heads, kv_heads, head_dim = 4, 2, 64
+    rng = np.random.default_rng(len(path))
+    lengths = [(300, 170), (90, 90)]
+    queries = sum(n for _, n in lengths)
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n, _ in lengths]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    wide = rounded(rng.normal(size=(queries, 3 * heads * head_dim)) * 2.0, dtype)
+    gate = dev(wide, dtype)[:, heads * head_dim:2 * heads * head_dim]
+    factor = (1.0 / (1.0 + np.exp(-wide[:, heads * head_dim:2 * heads * head_dim]))).reshape(queries, heads, head_dim)
+
+    def run(with_gate):
+        if path.startswith("general"):
+            return run_attention(ops, dtype, q, k, v, lengths, 16, 0.125, chunk=128, gate=with_gate)
+        ops.KEY_SHARES = 3 if path.endswith("shared keys") else None
+        try:
+            return run_flash(ops, q, k, v, lengths, 16, 0.125, chunk=128, kernel=path.split()[0], gate=with_gate)
+        finally:
+            ops.KEY_SHARES = None
+    bare, gated = run(None), run(gate)
+    assert np.abs(gated - bare * factor).max() < tol(dtype, 1e-6, 1.5e-2)
+    assert np.abs(gated - bare).max() > 0.1
+
+
 def test_attention_does_not_depend_on_the_cut(ops):
     """float32: the same query gives the same bits alone, in a tile of 16 and
     beside other requests."""
@@ -429,7 +458,8 @@ def test_attention_does_not_depend_on_the_cut(ops):
     assert np.array_equal(part[37:], whole[total - 12:total - 9])
 
 
-def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kernel="mma", tile=128, chunk=0):
+def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kernel="mma", tile=128, chunk=0,
+              gate=None):
     """A tensor-core prompt kernel ("mma": warp-level, "tcgen05": TMA and
     tensor memory) on requests whose last ``queries`` positions are the
     queries (bfloat16), cut into tiles of up to ``tile`` tokens."""
@@ -459,7 +489,7 @@ def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kerne
     ops.flash_prefill(q_all, dev(host_cache, dtype), out, dev(tables, torch.int32),
                       dev([t[0] for t in tiles], torch.int32), dev([t[1] for t in tiles], torch.int32),
                       dev([t[2] for t in tiles], torch.int32), dev(positions, torch.int32), scale, window,
-                      kernel=kernel, chunk=chunk)
+                      kernel=kernel, chunk=chunk, gate=gate)
     ops.check_status("cuda")
     return out.cpu().double().numpy()
 
