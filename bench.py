@@ -748,7 +748,7 @@ def design(args):
     rng = np.random.default_rng(0)
     out = {"design": "mekazen", "beside": "qwen3", "dtype": "bf16", "layers": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
            "prompt_len": args.prompt_len, "chunk": args.chunk or args.context, "peaks": peak_source, "sizes": {}}
-    for size, (hidden, heads, kv_heads, dim, inter) in DESIGN_SIZES.items():
+    for size, (hidden, heads, kv_heads, dim, inter) in ({} if args.kernels_only else DESIGN_SIZES).items():
         configs = {
             "mekazen": parse_config(_mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or args.context)),
             "qwen3": parse_config(dict(_qwen3(DESIGN_LAYERS, hidden, heads, kv_heads, inter, False),
@@ -813,6 +813,7 @@ def design(args):
                 "frac_of_copy_bandwidth": bytes_moved / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
 
     kernels = {}
+    ops.require_cuda()
     hidden, heads, kv_heads, dim, inter = DESIGN_SIZES["8b-layers"]
     bf16 = torch.bfloat16
     for tokens in (8, args.prompt_len * 4):
@@ -900,6 +901,8 @@ def main():
     parser.add_argument("--design", choices=("mekazen",),
                         help="another decoder design beside Qwen3 at equal layer sizes, and its kernels beside their like")
     parser.add_argument("--chunk", type=int, default=0, help="--design: positions per chunk of the mask (0: the context)")
+    parser.add_argument("--kernels-only", action="store_true",
+                        help="--design: only the design's kernels beside their like (a small case for a profiler)")
     args = parser.parse_args()
 
     if args.impl == "reference":

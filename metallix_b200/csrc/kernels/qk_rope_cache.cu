@@ -255,11 +255,17 @@ qk_norm_rope_cache_warp_kernel(
 // The norm over a token's whole projection: one RMS over all query heads'
 // values (weights [heads * head_dim]) and one over all key heads', then the
 // rotation head by head, q to q_out, k and v into the cache. One block per
-// token; the two rows wait in shared memory as float32 between the sum of
-// squares and the rotation, whose partner may lie anywhere in the head. V
-// values of T move as one access where rows are aligned for it (V = 1: any
-// layout).
-template <typename T, int V>
+// token, two passes over its rows: the sums of squares, then norm, rotation
+// and the writes, for which a thread fetches its values a second time (they
+// come from the cache of the first pass; keeping them in shared memory cost
+// more in stores and loads than it saved) and a rotation partner that lies
+// elsewhere in the head by a load of its own. V values of T move as one
+// access where rows are aligned for it (V = 1: any layout). HELD (a step of
+// few tokens, rows of at most 4 * 256 * V values): a thread keeps its up to
+// four vectors of q and of k in registers instead, every load of the first
+// pass in flight at once, since such a step waits for trips to memory and
+// not for bandwidth.
+template <typename T, int V, bool HELD>
 __global__ void __launch_bounds__(256)
 qk_rownorm_rope_cache_kernel(
     const T* __restrict__ q_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
@@ -269,15 +275,12 @@ qk_rownorm_rope_cache_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     int rotary_dim, int interleaved, int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
     float eps, int* status) {
-  extern __shared__ __align__(16) float rows[];   // the q row, then the k row
   __shared__ float scratch[66];
   using Values = Pack<T, V>;
   chain_release();
   // Up to chain_wait(): the step's integers only.
   const int t = blockIdx.x;
   const int q_width = heads * head_dim, k_width = kv_heads * head_dim;
-  float* q_row = rows;
-  float* k_row = rows + q_width;
   int pos = positions[t];
   const bool rotate = cos_table != nullptr;
   if (rotate && (pos < 0 || pos >= table_positions)) {
@@ -303,34 +306,59 @@ qk_rownorm_rope_cache_kernel(
   const T* v_src = behind_wait(v_in) + t * v_stride;
 
   float q_sum = 0.0f, k_sum = 0.0f;
-  if (q_out != nullptr) {
-    for (int i = threadIdx.x * V; i < q_width; i += blockDim.x * V) {
-      const Values in = *reinterpret_cast<const Values*>(q_src + i);
+  constexpr int R = HELD ? 4 : 1;
+  Values q_held[R], k_held[R], v_held[R];
+  if (HELD) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float x = to_float(in.v[j]);
-        q_row[i + j] = x;
-        q_sum += x * x;
+    for (int r = 0; r < R; ++r) {   // every load first
+      const int i = (threadIdx.x + r * blockDim.x) * V;
+      if (q_out != nullptr && i < q_width) q_held[r] = *reinterpret_cast<const Values*>(q_src + i);
+      if (key_page != nullptr && i < k_width) {
+        k_held[r] = *reinterpret_cast<const Values*>(k_src + i);
+        v_held[r] = *reinterpret_cast<const Values*>(v_src + i);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = (threadIdx.x + r * blockDim.x) * V;
+      if (q_out != nullptr && i < q_width) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) q_sum += to_float(q_held[r].v[j]) * to_float(q_held[r].v[j]);
+      }
+      if (key_page != nullptr && i < k_width) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) k_sum += to_float(k_held[r].v[j]) * to_float(k_held[r].v[j]);
+        const int kv = i / head_dim, d = i - kv * head_dim;
+        *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) = v_held[r];   // as projected
+      }
+    }
+  } else {
+    if (q_out != nullptr) {
+      for (int i = threadIdx.x * V; i < q_width; i += blockDim.x * V) {
+        const Values in = *reinterpret_cast<const Values*>(q_src + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float x = to_float(in.v[j]);
+          q_sum += x * x;
+        }
+      }
+    }
+    if (key_page != nullptr) {
+      for (int i = threadIdx.x * V; i < k_width; i += blockDim.x * V) {
+        const Values in = *reinterpret_cast<const Values*>(k_src + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float x = to_float(in.v[j]);
+          k_sum += x * x;
+        }
+        // values are stored as projected
+        const int kv = i / head_dim, d = i - kv * head_dim;
+        *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) =
+            *reinterpret_cast<const Values*>(v_src + i);
       }
     }
   }
-  if (key_page != nullptr) {
-    for (int i = threadIdx.x * V; i < k_width; i += blockDim.x * V) {
-      const Values in = *reinterpret_cast<const Values*>(k_src + i);
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float x = to_float(in.v[j]);
-        k_row[i + j] = x;
-        k_sum += x * x;
-      }
-      // values are stored as projected
-      const int kv = i / head_dim, d = i - kv * head_dim;
-      *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) =
-          *reinterpret_cast<const Values*>(v_src + i);
-    }
-  }
-  // Both sums at once; the barriers also make the rows visible to every thread.
-  {
+  {  // both sums at once
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
     q_sum = warp_sum(q_sum);
     k_sum = warp_sum(k_sum);
@@ -347,13 +375,13 @@ qk_rownorm_rope_cache_kernel(
   }
   const int half = rotary_dim >> 1;
 
-  auto finish = [&](const float* row, int width, float sum, const float* weight, bool is_q) {
+  auto finish = [&](const T* row, const Values (&held)[R], int width, float sum, const float* weight, bool is_q) {
     const float scale = weight != nullptr ? rsqrtf(sum / static_cast<float>(width) + eps) : 1.0f;
-    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+    auto one = [&](int i, const Values& in) {
       const int h = i / head_dim, d0 = i - h * head_dim;   // V divides head_dim: a vector stays in one head
       float x[V];
 #pragma unroll
-      for (int j = 0; j < V; ++j) x[j] = row[i + j] * scale;
+      for (int j = 0; j < V; ++j) x[j] = to_float(in.v[j]) * scale;
       if (weight != nullptr) {
         if (V % 4 == 0) {
 #pragma unroll
@@ -388,7 +416,7 @@ qk_rownorm_rope_cache_kernel(
               const bool first = interleaved ? (d & 1) == 0 : d < half;
               const int pair = interleaved ? d >> 1 : (first ? d : d - half);
               const int partner = i + j + (interleaved ? (first ? 1 : -1) : (first ? half : -half));
-              const float y = row[partner] * scale * (weight != nullptr ? weight[partner] : 1.0f);
+              const float y = to_float(row[partner]) * scale * (weight != nullptr ? weight[partner] : 1.0f);
               const float c = cos_table[static_cast<size_t>(pos) * half + pair];
               const float s = sin_table[static_cast<size_t>(pos) * half + pair];
               x[j] = first ? x[j] * c - y * s : x[j] * c + y * s;
@@ -401,10 +429,19 @@ qk_rownorm_rope_cache_kernel(
       for (int j = 0; j < V; ++j) out.v[j] = from_float<T>(x[j]);
       if (is_q) *reinterpret_cast<Values*>(q_out + static_cast<size_t>(t) * width + i) = out;
       else *reinterpret_cast<Values*>(key_page + h * head_stride + d0) = out;
+    };
+    if constexpr (HELD) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int i = (threadIdx.x + r * blockDim.x) * V;
+        if (i < width) one(i, held[r]);
+      }
+    } else {
+      for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) one(i, *reinterpret_cast<const Values*>(row + i));
     }
   };
-  if (q_out != nullptr) finish(q_row, q_width, q_sum, q_weight, true);
-  if (key_page != nullptr) finish(k_row, k_width, k_sum, k_weight, false);
+  if (q_out != nullptr) finish(q_src, q_held, q_width, q_sum, q_weight, true);
+  if (key_page != nullptr) finish(k_src, k_held, k_width, k_sum, k_weight, false);
 }
 
 }  // namespace mxb
@@ -433,11 +470,13 @@ MXB_API int mxb_qk_norm_rope_cache(
     const bool wide = head_dim % vector == 0 && aligned(q_in, q_stride) && aligned(k_in, k_stride) &&
                       aligned(v_in, v_stride) && aligned(q_out, 0) && aligned(cache, 0) &&
                       aligned(q_weight, 0) && aligned(k_weight, 0);
-    const size_t shared = static_cast<size_t>(heads + kv_heads) * head_dim * sizeof(float);
+    const size_t shared = 0;
     cudaError_t launch_status = cudaSuccess;
-#define ROW_LAUNCH(T, V) do { \
-      auto kernel = qk_rownorm_rope_cache_kernel<T, V>; \
-      if (shared > 48 * 1024) launch_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
+    // few tokens and rows that four vectors a thread cover: the loads of a row all at once
+    const bool few = tokens <= 256 && heads * head_dim <= 4 * 256 * (wide ? vector : 1);
+#define ROW_LAUNCH(T, V) do { if (few) ROW_LAUNCH_AS(T, V, true); else ROW_LAUNCH_AS(T, V, false); } while (0)
+#define ROW_LAUNCH_AS(T, V, HELD) do { \
+      auto kernel = qk_rownorm_rope_cache_kernel<T, V, HELD>; \
       if (launch_status == cudaSuccess) launch_status = launch_chained(kernel, dim3(tokens), dim3(256), shared, stream, \
         static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, v_stride, \
         static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, sin_table, \
@@ -445,6 +484,7 @@ MXB_API int mxb_qk_norm_rope_cache(
     if (dtype == kF32) { if (wide) ROW_LAUNCH(float, 4); else ROW_LAUNCH(float, 1); }
     else { if (wide) ROW_LAUNCH(__nv_bfloat16, 8); else ROW_LAUNCH(__nv_bfloat16, 1); }
 #undef ROW_LAUNCH
+#undef ROW_LAUNCH_AS
     return static_cast<int>(launch_status);
   }
   const bool vector_ok = aligned(q_in, q_stride) && aligned(k_in, k_stride) && aligned(v_in, v_stride) &&

@@ -36,7 +36,9 @@ __device__ __forceinline__ void sn_store4(__nv_bfloat16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename TDelta, typename TOut, bool VEC4>
+// PARTS: the delta comes in parts (their loads in flight together take
+// registers that the common case, a whole delta, leaves to more resident blocks).
+template <typename TDelta, typename TOut, bool VEC4, bool PARTS>
 __global__ void __launch_bounds__(256)
 postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ delta, int parts, size_t part_stride,
                             const float* __restrict__ w_post, float eps_post, TOut* __restrict__ y,
@@ -48,6 +50,14 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ de
   chain_release();
   const size_t base = static_cast<size_t>(blockIdx.x) * size;
   const int first = threadIdx.x * V, step = blockDim.x * V;
+  // The norms' weights for the thread's first values are fetched before the
+  // wait for the kernel that produces the delta (for rows up to 4 * blockDim.x
+  // wide that is all of them).
+  float4 first_post = make_float4(0.0f, 0.0f, 0.0f, 0.0f), first_next = first_post;
+  if (VEC4 && first < size) {
+    first_post = sn_load4(w_post + first);
+    if (y != nullptr) first_next = sn_load4(w_next + first);
+  }
   chain_wait();
   float* row = behind_wait(x) + base;            // both written by kernels ahead of this one
   const TDelta* d_row = behind_wait(delta) + base;
@@ -56,7 +66,7 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ de
   for (int i = first; i < size; i += step) {
     if (VEC4) {
       float4 d = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      if (parts == 1) {
+      if (!PARTS) {
         d = sn_load4(d_row + i);
       } else {
         // a loop of one load and one add would make a trip to memory per part
@@ -73,7 +83,7 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ de
       sum += d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w;
     } else {
       float d = 0.0f;
-      for (int part = 0; part < parts; ++part) d += to_float(d_row[part * part_stride + i]);
+      for (int part = 0; part < (PARTS ? parts : 1); ++part) d += to_float(d_row[part * part_stride + i]);
       held[i] = d;
       sum += d * d;
     }
@@ -83,7 +93,7 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ de
   sum = 0.0f;
   for (int i = first; i < size; i += step) {
     if (VEC4) {
-      const float4 d = *reinterpret_cast<const float4*>(held + i), g = sn_load4(w_post + i);
+      const float4 d = *reinterpret_cast<const float4*>(held + i), g = i == first ? first_post : sn_load4(w_post + i);
       float4 v = sn_load4(row + i);
       v.x += d.x * scale_post * g.x; v.y += d.y * scale_post * g.y;
       v.z += d.z * scale_post * g.z; v.w += d.w * scale_post * g.w;
@@ -103,7 +113,7 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ de
   TOut* dst = y + base;
   for (int i = first; i < size; i += step) {
     if (VEC4) {
-      const float4 v = *reinterpret_cast<const float4*>(held + i), g = sn_load4(w_next + i);
+      const float4 v = *reinterpret_cast<const float4*>(held + i), g = i == first ? first_next : sn_load4(w_next + i);
       sn_store4(dst + i, make_float4(v.x * scale_next * g.x, v.y * scale_next * g.y, v.z * scale_next * g.z,
                                      v.w * scale_next * g.w));
     } else {
@@ -174,9 +184,11 @@ MXB_API int mxb_postnorm_add_rmsnorm(float* x, const void* delta, int delta_dtyp
     threads = 32;
     while (threads * 4 < size && threads < 256) threads <<= 1;
   }
-#define LAUNCH(TD, TO) do { if (vec4) LAUNCH_AS(TD, TO, true); else LAUNCH_AS(TD, TO, false); } while (0)
-#define LAUNCH_AS(TD, TO, VEC) do { \
-    auto kernel = postnorm_add_rmsnorm_kernel<TD, TO, VEC>; \
+#define LAUNCH(TD, TO) do { \
+    if (vec4) { if (parts > 1) LAUNCH_AS(TD, TO, true, true); else LAUNCH_AS(TD, TO, true, false); } \
+    else { if (parts > 1) LAUNCH_AS(TD, TO, false, true); else LAUNCH_AS(TD, TO, false, false); } } while (0)
+#define LAUNCH_AS(TD, TO, VEC, MANY) do { \
+    auto kernel = postnorm_add_rmsnorm_kernel<TD, TO, VEC, MANY>; \
     if (shared > 48 * 1024) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
     if (e == cudaSuccess) e = launch_chained(kernel, dim3(rows), dim3(threads), shared, stream, x, static_cast<const TD*>(delta), \
                                              parts, part_stride, w_post, eps_post, static_cast<TO*>(y), w_next, eps_next, size); } while (0)
