@@ -724,8 +724,8 @@ DESIGN_LAYERS, DESIGN_VOCAB = 8, 32768
 
 def _mekazen(hidden, heads, kv_heads, dim, inter, chunk):
     mixer = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": chunk}, "scale": dim ** -0.5,
-             "vdim": dim, "rot": {"base": 1.0e6, "dims": dim // 2,
-                                  "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+             "vdim": dim, "rot": {"base": 5.0e5, "dims": dim // 2,
+                                  "scaling": {"factor": 32.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     layer = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": inter}}
     return {"architecture": "Mekazen", "vocab": DESIGN_VOCAB, "width": hidden, "norm": {"eps": 1e-6},
             "logit_softcap": 30.0, "layers": [layer] * DESIGN_LAYERS}

@@ -3,13 +3,13 @@
 A Mekazen model is a list of layers, each with sizes of its own. A layer is
 norm -> attention -> norm -> residual sum, then (unless its ``mlp`` is null)
 norm -> gated feed-forward -> norm -> residual sum. Its attention has no value
-projection (the values are the keys as projected), one RMS norm over the whole
-query projection and one over the whole key projection, a rotation of
-neighbouring pairs over the first ``rot.dims`` values of a head with a
-three-band stretch of the long wavelengths, a mask of chunks counted from
-position 0, and a sigmoid gate over the concatenated heads. The logits pass a
-tanh cap. Norm weights of the layers and of the model are stored around zero
-(the factor is 1 + w); the query and key norms store the factor itself.
+projection: the raw output of the key projection doubles as the values. q and
+k are each normalised across all their heads at once, rotated in neighbouring
+pairs over the first ``rot.dims`` values of a head (long wavelengths stretched
+in three bands), masked so that a query only reaches back to the last absolute
+multiple of ``mask.size``, and the heads' output is gated by a sigmoid. The
+logits pass a tanh cap. The layers' and the model's norms are zero-centred in
+the file (factor = 1 + w); the query and key norms hold the factor itself.
 
 ``config.json``::
 
@@ -97,7 +97,7 @@ class MekazenLayer:
             raise ConfigError("InvalidGroupedQueryLayout", f"{at}: {heads} query heads over {kv_heads} key/value heads")
         if dim % 2:
             raise ConfigError("OddHeadDimension", f"{at}.dim {dim}")
-        # the values are the keys as projected: their width is the keys'
+        # the key projection's output serves as the values: one width for both
         if mixer.get("vdim", dim) != dim:
             raise ConfigError("InvalidValueWidth", f"{at}.vdim {mixer.get('vdim')!r} must equal dim {dim}")
         scale = _number(mixer, "scale", at)
@@ -248,7 +248,7 @@ class MekazenConfig:
         spec.validate()
         return spec
 
-    # --------------------------------------------------------- tensor contract
+    # ------------------------------------------------ tensors of a checkpoint
     def tensor_shapes(self) -> Dict[str, tuple]:
         w = self.width
         shapes: Dict[str, tuple] = {"embed": (self.vocab, w)}

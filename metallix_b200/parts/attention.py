@@ -8,9 +8,9 @@ key/value head j // (heads / kv_heads); then the output projection
 
 Variants, each a parameter: the norms of q and k may run over a token's whole
 projection instead of head by head (``qk_norm_scope="projection"``); a model
-without a value projection takes its values from the keys as projected, before
-norm and rotation (no ``v_proj``); ``chunk`` lets a query see only the keys of
-its own chunk of that many positions, counted from position 0 of the sequence;
+without a value projection reuses the key projection's raw output (ahead of
+its norm and rotation) as the values (no ``v_proj``); ``chunk`` lets a query
+reach back only to the last absolute multiple of that many positions;
 ``gate_proj`` multiplies the concatenated heads by sigmoid(a Wg^T) ahead of the
 output projection.
 
@@ -128,7 +128,7 @@ class GQAttention:
             raise ValueError(f"head_dim {self.head_dim}: the attention kernels take even sizes up to 256")
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
-        # v_proj absent: the values are the keys as projected. gate_proj: an
+        # v_proj absent: the key projection's raw output is the values too. gate_proj: an
         # output gate over the concatenated heads, from the mixer's own input.
         self.own_values = spec.get("v_proj") is not None
         self.gated = spec.get("gate_proj") is not None

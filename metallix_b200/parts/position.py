@@ -8,11 +8,11 @@ f_i = theta^(-2i / rotary_dim): (a, b) -> (a cos - b sin, b cos + a sin); the
 values beyond ``rotary_dim`` pass unchanged.
 
 ``scaling`` (optional) stretches the long wavelengths for contexts beyond
-those a model was trained on, by a rule of three bands over the wavelength
-l_i = 2 pi / f_i: with ``original`` positions, a ``factor`` and the two band
-edges ``low`` < ``high``, a frequency is kept where l_i < original / high,
-divided by ``factor`` where l_i > original / low, and in between blended,
-(1 - s) f_i / factor + s f_i with s = (original / l_i - low) / (high - low).
+those a model was trained on. Let n_i = original * f_i / (2 pi) be the number
+of full turns pair i makes over ``original`` positions. A pair that turns more
+than ``high`` times keeps its frequency; one that turns fewer than ``low``
+times gets f_i / factor; in between the two are mixed, f_i (s + (1 - s) /
+factor) with s = (n_i - low) / (high - low) rising from 0 to 1.
 
 Angles are formed in float64 (position times frequency), cos and sin are
 rounded once to float32 tables that the kernels index by position.
@@ -39,11 +39,10 @@ def rotary_frequencies(theta: float, rotary_dim: int, scaling: Optional[Mapping]
         original = float(scaling["original"])
         if not (factor > 0.0 and high > low and original > 0.0):
             raise ValueError(f"rotary scaling needs factor > 0, high > low and original > 0, got {dict(scaling)}")
-        wavelength = 2.0 * math.pi / frequency
-        blend = (original / wavelength - low) / (high - low)
-        between = (1.0 - blend) * frequency / factor + blend * frequency
-        frequency = torch.where(wavelength < original / high, frequency,
-                                torch.where(wavelength > original / low, frequency / factor, between))
+        turns = original * frequency / (2.0 * math.pi)
+        share = (turns - low) / (high - low)
+        mixed = frequency * (share + (1.0 - share) / factor)
+        frequency = torch.where(turns > high, frequency, torch.where(turns < low, frequency / factor, mixed))
     return frequency
 
 

@@ -149,8 +149,8 @@ def test_configuration_round_trip_and_registry():
 
 
 def test_random_weights_follow_how_a_norm_is_stored(tmp_path):
-    """Norms stored around zero are drawn around zero, the query and key norms
-    around one; a checkpoint with a tensor too many or of the wrong shape is refused."""
+    """Zero-centred norms are drawn about zero, the query and key norms
+    about one; a checkpoint with a tensor too many or of the wrong shape is refused."""
     from metallix_b200.config import MekazenConfig
     from metallix_b200.weights import CheckpointError, load_tensors, random_tensors, write_model_folder
     config = MekazenConfig.from_dict(SMALL)
