@@ -658,7 +658,12 @@ def workload(args):
         ops.check_status("cuda")
         return 0
 
-    config = parse_config(dict(raw, num_hidden_layers=layers))
+    if args.design:   # the same workloads on the other design, at this shape's layer sizes
+        hidden, heads, kv_heads, dim, inter = DESIGN_SIZES[{"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape]]
+        other = _mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or 4096)
+        config = parse_config(dict(other, layers=other["layers"][:1] * layers))
+    else:
+        config = parse_config(dict(raw, num_hidden_layers=layers))
     pages = args.batch * (-(-(args.prompt_len + 64) // args.page_tokens) + 1) + 64 * 16 // args.page_tokens
     engine = Engine.from_random(config, 0, dtype="bfloat16", page_tokens=args.page_tokens, num_pages=pages,
                                 max_requests=args.batch + 2, max_context=args.max_context or max(4096, args.prompt_len + 256),
@@ -914,7 +919,7 @@ def main():
     if args.decode_resident is not None:
         from metallix_b200 import ops
         ops.set_decode_resident_blocks(args.decode_resident, max(args.decode_many, args.decode_resident))
-    if args.design:
+    if args.design and not args.workload:
         return design(args)
     if args.workload:
         return workload(args)

@@ -43,6 +43,8 @@ MAX_POSITIONS = 1 << 17   # the configuration names no limit; tables and graphs 
 
 def _count(raw: Mapping[str, Any], key: str, where: str) -> int:
     value = raw.get(key)
+    if isinstance(value, float) and value.is_integer():
+        value = int(value)    # a writer that knows only one kind of number
     if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
         raise ConfigError("MissingDimension", f"{where}.{key} must be a positive integer, got {value!r}")
     return value
@@ -178,7 +180,7 @@ class MekazenConfig:
         if eps <= 0.0:
             raise ConfigError("InvalidRmsNormEpsilon", str(eps))
         cap = 0.0
-        if raw.get("logit_softcap") is not None:
+        if raw.get("logit_softcap"):     # absent, null or 0: no cap
             cap = _number(raw, "logit_softcap", "config")
             if cap <= 0.0:
                 raise ConfigError("Json", f"logit_softcap must be positive, got {cap}")
@@ -189,6 +191,14 @@ class MekazenConfig:
                    layers=tuple(MekazenLayer.from_dict(layer, f"layers[{i}]") for i, layer in enumerate(layers)))
 
     # ------------------------------------------------------------ derived facts
+    @property
+    def vocab_size(self) -> int:      # the names every family answers to
+        return self.vocab
+
+    @property
+    def hidden_size(self) -> int:
+        return self.width
+
     def kv_bytes_per_token(self, bytes_per_value: int) -> int:
         return sum(2 * layer.kv_heads * layer.dim * bytes_per_value for layer in self.layers)
 

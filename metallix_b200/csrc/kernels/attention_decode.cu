@@ -954,12 +954,12 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
   chain_wait();
   base = behind_wait(base);  // the partial results are written by the kernel ahead of this one
   float m = kDecodeMinusHuge, acc = 0.0f, l = 0.0f;
-  for (int chunk = 0; chunk < splits; chunk += kMergeSplits) {
+  for (int round = 0; round < splits; round += kMergeSplits) {
     float ms[kMergeSplits], ls[kMergeSplits], values[kMergeSplits];
 #pragma unroll
     for (int j = 0; j < kMergeSplits; ++j) {
-      const bool live = chunk + j < splits;
-      const float* p = base + static_cast<size_t>(live ? chunk + j : 0) * stride;
+      const bool live = round + j < splits;
+      const float* p = base + static_cast<size_t>(live ? round + j : 0) * stride;
       ms[j] = live ? p[head_dim] : kDecodeMinusHuge;
       ls[j] = live ? p[head_dim + 1] : 0.0f;
       values[j] = live ? p[d] : 0.0f;

@@ -107,11 +107,11 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
 #pragma unroll
       for (int h = 0; h < HD / 64; ++h) gates[h] = *reinterpret_cast<const __nv_bfloat162*>(g + h * 64);
     }
-    for (int chunk = 0; chunk < splits; chunk += kChunk) {
-      const int live = min(kChunk, splits - chunk);
+    for (int round = 0; round < splits; round += kChunk) {
+      const int live = min(kChunk, splits - round);
       float mine = minus_huge, mine_sum = 0.0f;
       if (lane < live) {
-        const float2 stats = *reinterpret_cast<const float2*>(base + static_cast<size_t>(chunk + lane) * stride + HD);
+        const float2 stats = *reinterpret_cast<const float2*>(base + static_cast<size_t>(round + lane) * stride + HD);
         mine = stats.x;
         mine_sum = stats.y;
       }
@@ -120,7 +120,7 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
       auto fetch = [&](float2 (&into)[kBatch][HD / 64], int from) {
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
-          const float* p = base + static_cast<size_t>(chunk + (from + j < live ? from + j : 0)) * stride + lane * 2;
+          const float* p = base + static_cast<size_t>(round + (from + j < live ? from + j : 0)) * stride + lane * 2;
 #pragma unroll
           for (int h = 0; h < HD / 64; ++h)
             into[j][h] = from + j < live ? *reinterpret_cast<const float2*>(p + h * 64) : make_float2(0.0f, 0.0f);

@@ -61,6 +61,10 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Asks for the cache line of `p` without waiting for it: for what a kernel
+// will read behind its wait for the kernel ahead but that this kernel does not write.
+__device__ __forceinline__ void prefetch_line(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
 // An output gate over the concatenated heads (optional in every attention
 // kernel): the value a kernel is about to write for (token, head, d) times
 // sigmoid(gate[token * gate_stride + head * head_dim + d]), in float32.

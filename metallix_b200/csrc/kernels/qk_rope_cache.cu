@@ -260,12 +260,10 @@ qk_norm_rope_cache_warp_kernel(
 // come from the cache of the first pass; keeping them in shared memory cost
 // more in stores and loads than it saved) and a rotation partner that lies
 // elsewhere in the head by a load of its own. V values of T move as one
-// access where rows are aligned for it (V = 1: any layout). HELD (a step of
-// few tokens, rows of at most 4 * 256 * V values): a thread keeps its up to
-// four vectors of q and of k in registers instead, every load of the first
-// pass in flight at once, since such a step waits for trips to memory and
-// not for bandwidth.
-template <typename T, int V, bool HELD>
+// access where rows are aligned for it (V = 1: any layout). What a thread's
+// first vectors need besides the rows (norm weights, cosines and sines) is
+// asked into the cache ahead of the wait for the kernel that writes the rows.
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 qk_rownorm_rope_cache_kernel(
     const T* __restrict__ q_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
@@ -300,62 +298,45 @@ qk_rownorm_rope_cache_kernel(
     }
   }
   const size_t head_stride = static_cast<size_t>(page_tokens) * head_dim;   // from one head of a page to the next
+  {
+    const int i = threadIdx.x * V;   // the thread's first vector of q and of k
+    if (q_weight != nullptr && q_out != nullptr && i < q_width) prefetch_line(q_weight + i);
+    if (k_weight != nullptr && key_page != nullptr && i < k_width) prefetch_line(k_weight + i);
+    const int d0 = i % head_dim;
+    if (rotate && d0 < rotary_dim && i < q_width) {
+      const int pair = interleaved ? d0 >> 1 : (d0 < (rotary_dim >> 1) ? d0 : d0 - (rotary_dim >> 1));
+      prefetch_line(cos_table + static_cast<size_t>(pos) * (rotary_dim >> 1) + pair);
+      prefetch_line(sin_table + static_cast<size_t>(pos) * (rotary_dim >> 1) + pair);
+    }
+  }
   chain_wait();
   const T* q_src = behind_wait(q_in) + t * q_stride;   // written by the kernel ahead of this one
   const T* k_src = behind_wait(k_in) + t * k_stride;
   const T* v_src = behind_wait(v_in) + t * v_stride;
 
   float q_sum = 0.0f, k_sum = 0.0f;
-  constexpr int R = HELD ? 4 : 1;
-  Values q_held[R], k_held[R], v_held[R];
-  if (HELD) {
+  if (q_out != nullptr) {
+    for (int i = threadIdx.x * V; i < q_width; i += blockDim.x * V) {
+      const Values in = *reinterpret_cast<const Values*>(q_src + i);
 #pragma unroll
-    for (int r = 0; r < R; ++r) {   // every load first
-      const int i = (threadIdx.x + r * blockDim.x) * V;
-      if (q_out != nullptr && i < q_width) q_held[r] = *reinterpret_cast<const Values*>(q_src + i);
-      if (key_page != nullptr && i < k_width) {
-        k_held[r] = *reinterpret_cast<const Values*>(k_src + i);
-        v_held[r] = *reinterpret_cast<const Values*>(v_src + i);
+      for (int j = 0; j < V; ++j) {
+        const float x = to_float(in.v[j]);
+        q_sum += x * x;
       }
     }
+  }
+  if (key_page != nullptr) {
+    for (int i = threadIdx.x * V; i < k_width; i += blockDim.x * V) {
+      const Values in = *reinterpret_cast<const Values*>(k_src + i);
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int i = (threadIdx.x + r * blockDim.x) * V;
-      if (q_out != nullptr && i < q_width) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) q_sum += to_float(q_held[r].v[j]) * to_float(q_held[r].v[j]);
+      for (int j = 0; j < V; ++j) {
+        const float x = to_float(in.v[j]);
+        k_sum += x * x;
       }
-      if (key_page != nullptr && i < k_width) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) k_sum += to_float(k_held[r].v[j]) * to_float(k_held[r].v[j]);
-        const int kv = i / head_dim, d = i - kv * head_dim;
-        *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) = v_held[r];   // as projected
-      }
-    }
-  } else {
-    if (q_out != nullptr) {
-      for (int i = threadIdx.x * V; i < q_width; i += blockDim.x * V) {
-        const Values in = *reinterpret_cast<const Values*>(q_src + i);
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float x = to_float(in.v[j]);
-          q_sum += x * x;
-        }
-      }
-    }
-    if (key_page != nullptr) {
-      for (int i = threadIdx.x * V; i < k_width; i += blockDim.x * V) {
-        const Values in = *reinterpret_cast<const Values*>(k_src + i);
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float x = to_float(in.v[j]);
-          k_sum += x * x;
-        }
-        // values are stored as projected
-        const int kv = i / head_dim, d = i - kv * head_dim;
-        *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) =
-            *reinterpret_cast<const Values*>(v_src + i);
-      }
+      // values are stored as projected
+      const int kv = i / head_dim, d = i - kv * head_dim;
+      *reinterpret_cast<Values*>(key_page + (kv_heads + kv) * head_stride + d) =
+          *reinterpret_cast<const Values*>(v_src + i);
     }
   }
   {  // both sums at once
@@ -375,7 +356,7 @@ qk_rownorm_rope_cache_kernel(
   }
   const int half = rotary_dim >> 1;
 
-  auto finish = [&](const T* row, const Values (&held)[R], int width, float sum, const float* weight, bool is_q) {
+  auto finish = [&](const T* row, int width, float sum, const float* weight, bool is_q) {
     const float scale = weight != nullptr ? rsqrtf(sum / static_cast<float>(width) + eps) : 1.0f;
     auto one = [&](int i, const Values& in) {
       const int h = i / head_dim, d0 = i - h * head_dim;   // V divides head_dim: a vector stays in one head
@@ -430,18 +411,10 @@ qk_rownorm_rope_cache_kernel(
       if (is_q) *reinterpret_cast<Values*>(q_out + static_cast<size_t>(t) * width + i) = out;
       else *reinterpret_cast<Values*>(key_page + h * head_stride + d0) = out;
     };
-    if constexpr (HELD) {
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int i = (threadIdx.x + r * blockDim.x) * V;
-        if (i < width) one(i, held[r]);
-      }
-    } else {
-      for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) one(i, *reinterpret_cast<const Values*>(row + i));
-    }
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) one(i, *reinterpret_cast<const Values*>(row + i));
   };
-  if (q_out != nullptr) finish(q_src, q_held, q_width, q_sum, q_weight, true);
-  if (key_page != nullptr) finish(k_src, k_held, k_width, k_sum, k_weight, false);
+  if (q_out != nullptr) finish(q_src, q_width, q_sum, q_weight, true);
+  if (key_page != nullptr) finish(k_src, k_width, k_sum, k_weight, false);
 }
 
 }  // namespace mxb
@@ -472,11 +445,10 @@ MXB_API int mxb_qk_norm_rope_cache(
                       aligned(q_weight, 0) && aligned(k_weight, 0);
     const size_t shared = 0;
     cudaError_t launch_status = cudaSuccess;
-    // few tokens and rows that four vectors a thread cover: the loads of a row all at once
-    const bool few = tokens <= 256 && heads * head_dim <= 4 * 256 * (wide ? vector : 1);
-#define ROW_LAUNCH(T, V) do { if (few) ROW_LAUNCH_AS(T, V, true); else ROW_LAUNCH_AS(T, V, false); } while (0)
-#define ROW_LAUNCH_AS(T, V, HELD) do { \
-      auto kernel = qk_rownorm_rope_cache_kernel<T, V, HELD>; \
+    // few tokens and rows that one vector a thread covers: a thread per vector
+    const int vectors = heads * head_dim / (wide ? vector : 1);
+#define ROW_LAUNCH(T, V) do { \
+      auto kernel = qk_rownorm_rope_cache_kernel<T, V>; \
       if (launch_status == cudaSuccess) launch_status = launch_chained(kernel, dim3(tokens), dim3(256), shared, stream, \
         static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, v_stride, \
         static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, sin_table, \
@@ -484,7 +456,6 @@ MXB_API int mxb_qk_norm_rope_cache(
     if (dtype == kF32) { if (wide) ROW_LAUNCH(float, 4); else ROW_LAUNCH(float, 1); }
     else { if (wide) ROW_LAUNCH(__nv_bfloat16, 8); else ROW_LAUNCH(__nv_bfloat16, 1); }
 #undef ROW_LAUNCH
-#undef ROW_LAUNCH_AS
     return static_cast<int>(launch_status);
   }
   const bool vector_ok = aligned(q_in, q_stride) && aligned(k_in, k_stride) && aligned(v_in, v_stride) &&

@@ -65,6 +65,7 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restrict__ de
   float sum = 0.0f;
   for (int i = first; i < size; i += step) {
     if (VEC4) {
+      prefetch_line(row + i);   // the second pass reads it
       float4 d = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (!PARTS) {
         d = sn_load4(d_row + i);
@@ -230,3 +231,5 @@ MXB_API int mxb_softcap(float* x, float cap, long long count, cudaStream_t strea
   const unsigned blocks = static_cast<unsigned>((count + threads - 1) / threads);
   return static_cast<int>(launch_chained(softcap_kernel, dim3(blocks), dim3(threads), 0, stream, x, cap, count));
 }
+
+MXB_TIMELINE_EXPORT(mxb_timeline_sandwich_norms)

@@ -164,7 +164,7 @@ def set_chained_launches(enabled: bool) -> None:
         _chained = bool(enabled)
 
 
-TIMELINE_SOURCES = ("norms", "gemm_load", "gemm_stream", "qk_rope", "attention")
+TIMELINE_SOURCES = ("norms", "sandwich_norms", "gemm_load", "gemm_stream", "qk_rope", "attention")
 
 
 def timeline(reset: bool = True):
