@@ -157,7 +157,7 @@ class CacheManager {
       if (cfg.window == 0 && cfg.chunk == 0) continue;
       // The next query sits at position >= computed and sees keys
       // > position - window, so keys below computed - window + 1 are dead;
-      // it sees no key ahead of its own chunk, so keys below the start of the
+      // it sees no key before its own chunk, so keys below the start of the
       // chunk that holds position `computed` are dead too.
       int64_t first_needed = cfg.window > 0 ? r.computed - cfg.window + 1 : 0;
       if (cfg.chunk > 0) first_needed = std::max<int64_t>(first_needed, r.computed - r.computed % cfg.chunk);

@@ -198,7 +198,7 @@ def test_chunked_groups_give_pages_back():
         manager.check_invariants()
         computed = step + 1
         held.append([sum(1 for page in manager.table(1, g) if page >= 0) for g in range(3)])
-        # chunks of 10: pages wholly ahead of the chunk of the next position are gone
+        # chunks of 10: pages wholly before the chunk of the next position are gone
         first_needed = computed - computed % 10
         assert manager.first_live_page(1, 0) == first_needed // 4
         assert manager.first_live_page(1, 1) == 0
