@@ -1,18 +1,18 @@
 """metallix_b200: a small, whole inference engine for one B200.
 
 From a model folder (``config.json`` + safetensors) to the next token on one
-GPU, for the Qwen3 dense decoder and the Mekazen decoder: typed configuration and architecture
+GPU, for the Qwen3 dense decoder, the Mekazen decoder and the Zitezen decoder: typed configuration and architecture
 registry, by-name weight loading, layers put together from parts, a paged
 cache manager, one step function for mixed batches, a continuous-batching
 scheduler, sampling, and hand-written sm_100a kernels with a true float32 path.
 """
 from . import parts  # noqa: F401  (registers the built-in parts)
-from .config import ConfigError, MekazenConfig, Qwen3Config, parse_config, read_config
+from .config import ConfigError, MekazenConfig, Qwen3Config, ZitezenConfig, parse_config, read_config
 from .weights import CheckpointError, load_tensors, random_tensors, write_model_folder
 
 __version__ = "0.1.0"
 
-__all__ = ["ConfigError", "MekazenConfig", "Qwen3Config", "parse_config", "read_config", "CheckpointError",
+__all__ = ["ConfigError", "MekazenConfig", "Qwen3Config", "ZitezenConfig", "parse_config", "read_config", "CheckpointError",
            "load_tensors", "random_tensors", "write_model_folder", "Engine", "StepEntry",
            "generate"]
 

@@ -6,14 +6,16 @@ Accounting (which request holds which page, which pages are free) is the C++
 tables into what the kernels read.
 
 Device layout of a group of layers with the same needs:
-``[entries, pages, 2 (K, V), kv_heads, page_tokens, head_dim]`` in the compute
-dtype: one entry per layer of the group, so a page index means the same
+``[entries, pages, planes, kv_heads, page_tokens, head_dim]`` in the compute
+dtype (two planes: K and V; one plane: rows that serve as both): one entry per
+layer of the group, so a page index means the same
 positions in every layer of the group and one block table serves them all. The
 reference keeps K and V per layer as ``[slots, kv_heads, head_dim]``
 (crates/models/qwen/src/forward/paged.rs:135-146); here a head's rows of one
 page are contiguous so that a kernel reads a page of one head as one block.
 State entries are ``[request_slots, *state_shape]``, zeroed when a request is
-admitted.
+admitted. A mixer made of mixers has one need per member; each gets memory of
+its own under the key ``(entry, member index)``.
 """
 from __future__ import annotations
 
@@ -52,8 +54,8 @@ class PagedCache:
         reference sizes its pool from a byte budget the same way
         (crates/core/engine/src/blocks.rs:162-180)."""
         size = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * need.kv_heads * need.head_dim * page_tokens * size
-                   for need in needs if need is not None and need.kind == "kv_pages")
+        return sum(need.planes * need.kv_heads * need.head_dim * page_tokens * size
+                   for whole in needs if whole is not None for need in whole.flat() if need.kind == "kv_pages")
 
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_tokens: int, num_pages: int,
                  max_requests: int, dtype: torch.dtype, device, allocate: bool = True):
@@ -64,13 +66,21 @@ class PagedCache:
         self.page_tokens, self.max_requests = page_tokens, max_requests
         self.dtype, self.device = dtype, torch.device(device)
         self.groups: List[Group] = []
-        self.entry_group: Dict[int, int] = {}
-        self.entry_index: Dict[int, int] = {}
-        self.states: Dict[int, torch.Tensor] = {}
+        self.entry_group: Dict[object, int] = {}
+        self.entry_index: Dict[object, int] = {}
+        self.states: Dict[object, torch.Tensor] = {}
         self.needs = list(needs)
         by_key: Dict[tuple, Group] = {}
-        for entry, need in enumerate(self.needs):
-            if need is None or need.kind == "none":
+        keyed = []   # (key, need): an entry's own need, or one per member of a mixer made of mixers
+        for entry, whole in enumerate(self.needs):
+            if whole is None:
+                continue
+            if whole.kind == "several":
+                keyed.extend(((entry,) + path, need) for path, need in self._members(whole))
+            else:
+                keyed.append((entry, whole))
+        for entry, need in keyed:
+            if need.kind == "none":
                 continue
             if need.kind == "kv_pages":
                 key = need.group_key()
@@ -95,14 +105,23 @@ class PagedCache:
         if allocate:
             for group in self.groups:
                 group.pool = torch.zeros(
-                    (len(group.entries), group.num_pages, 2, group.need.kv_heads, page_tokens,
+                    (len(group.entries), group.num_pages, group.need.planes, group.need.kv_heads, page_tokens,
                      group.need.head_dim), dtype=dtype, device=self.device)
+
+    @staticmethod
+    def _members(need: CacheNeed, path: tuple = ()):
+        """(path of member indices, need) of every member that is not itself made of members."""
+        for index, member in enumerate(need.members):
+            if member.kind == "several":
+                yield from PagedCache._members(member, path + (index,))
+            else:
+                yield path + (index,), member
 
     # ------------------------------------------------------------------ facts
     def bytes_per_token(self) -> int:
         """Bytes of keys and values one position takes over all groups."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * g.need.kv_heads * g.need.head_dim * size * len(g.entries) for g in self.groups)
+        return sum(g.need.planes * g.need.kv_heads * g.need.head_dim * size * len(g.entries) for g in self.groups)
 
     def pool_bytes(self) -> int:
         return sum(g.pool.numel() * g.pool.element_size() for g in self.groups if g.pool is not None)
@@ -134,9 +153,16 @@ class PagedCache:
 
     def view(self, entry: int, write: bool, tables: Dict[int, torch.Tensor],
              slots: Dict[int, torch.Tensor]) -> CacheView:
-        need = self.needs[entry]
+        return self._view(entry, self.needs[entry], write, tables, slots)
+
+    def _view(self, entry, need: Optional[CacheNeed], write: bool, tables, slots) -> CacheView:
         if need is None or need.kind == "none":
             return CacheView(need=need or CacheNeed("none"), write=False)
+        if need.kind == "several":
+            path = entry if isinstance(entry, tuple) else (entry,)
+            return CacheView(need=need, write=write, members=[
+                self._view(path + (index,), member, write, tables, slots)
+                for index, member in enumerate(need.members)])
         if need.kind == "state":
             return CacheView(need=need, state=self.states[entry], write=write)
         group = self.groups[self.entry_group[entry]]

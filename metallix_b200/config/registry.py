@@ -17,6 +17,7 @@ from typing import Any, Dict, Mapping, Optional, Type
 
 from .mekazen import MekazenConfig
 from .qwen3 import ConfigError, Qwen3Config
+from .zitezen import ZitezenConfig
 
 
 @dataclass(frozen=True)
@@ -128,3 +129,6 @@ register(QWEN3)
 MEKAZEN = ModelFamily(architecture=MekazenConfig.ARCHITECTURE, model_type=MekazenConfig.MODEL_TYPE,
                       kind="mekazen", config_class=MekazenConfig)
 register(MEKAZEN)
+ZITEZEN = ModelFamily(architecture=ZitezenConfig.ARCHITECTURE, model_type=ZitezenConfig.MODEL_TYPE,
+                      kind="zitezen", config_class=ZitezenConfig)
+register(ZITEZEN)

@@ -80,9 +80,12 @@ class CacheNeed:
     ``head_dim`` for every position (``window is None``) or for the last
     ``window`` positions; with ``chunk`` only the positions of the chunk of
     that many positions (counted from position 0) the next query lies in are
-    ever read again. ``kind == "state"``: ``state_shape`` values of fixed
+    ever read again. ``planes`` is 2 for keys and values, 1 for a pool with
+    one row per position that serves as both (a latent that all heads share).
+    ``kind == "state"``: ``state_shape`` values of fixed
     size per request, zeroed when the request is admitted. ``kind == "none"``:
-    the mixer keeps nothing between steps.
+    the mixer keeps nothing between steps. ``kind == "several"``: a mixer made
+    of mixers; ``members`` are their needs, in the mixer's own order.
     """
 
     kind: str
@@ -92,10 +95,23 @@ class CacheNeed:
     chunk: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
+    planes: int = 2
+    members: Tuple["CacheNeed", ...] = ()
 
     def group_key(self) -> tuple:
         return (self.kind, self.kv_heads, self.head_dim, self.window, self.chunk,
-                tuple(self.state_shape), self.state_dtype)
+                tuple(self.state_shape), self.state_dtype, self.planes,
+                tuple(member.group_key() for member in self.members))
+
+    def flat(self) -> Tuple["CacheNeed", ...]:
+        """The needs that take memory: this one, or a mixer-of-mixers' members (to any depth)."""
+        if self.kind != "several":
+            return (self,)
+        return tuple(need for member in self.members for need in member.flat())
+
+    def has_state(self) -> bool:
+        """Whether a step advances something that running it twice would advance twice."""
+        return any(need.kind == "state" for need in self.flat())
 
 
 @dataclass(frozen=True)
@@ -111,6 +127,10 @@ class ModelSpec:
     order: Tuple[LayerRun, ...]
     final_norm: PartSpec
     head: PartSpec
+    # 0: one residual stream [tokens, hidden]. s >= 1: s copies of it,
+    # [tokens, s, hidden], all equal to the embedding at the start and summed at
+    # the end, which blocks of a hyper-connection arrangement read and write.
+    streams: int = 0
 
     def num_cache_entries(self) -> int:
         return max(run.cache_entry() for run in self.order) + 1

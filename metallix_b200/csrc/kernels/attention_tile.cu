@@ -14,6 +14,14 @@
 // :1067-1076, :1176-1184): s = (q k^T) * scale, causal with the diagonal at the
 // query's own position, optional window (key > position - window) and chunk (key >= position - position % chunk), softmax
 // over keys, query head j reads key/value head j / (heads / kv_heads).
+//
+// Further parameters, each off by default: `softcap` c bounds a score to
+// (-c, c) ahead of the softmax, s <- c tanh(s / c); the pool may hold one plane
+// per page instead of two (`planes` 1: the values are the first `value_dim`
+// values of the key rows themselves, what attention through a shared latent
+// needs); `value_dim` (at most head_dim) is how many values of a value row
+// make up the output, out being [tokens, heads, value_dim]; the output gate
+// may be one number per (token, head) (`gate_per_head`) instead of one per value.
 #include "common.cuh"
 
 namespace mxb {
@@ -31,7 +39,7 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
                             const int* __restrict__ tile_length, const int* __restrict__ positions,
                             int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                             int window, int chunk, float scale, const T* __restrict__ gate, long long gate_stride,
-                            int* status) {
+                            int planes, int value_dim, float softcap, int gate_per_head, int* status) {
   extern __shared__ float shared[];
   float* sQ = shared;                                   // [16][head_dim]
   float* sK = sQ + kTileQueries * head_dim;             // [32][head_dim + 1]
@@ -76,9 +84,9 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
         if (page < 0 || page >= num_pages) {
           atomicOr(status, kStatusBadPage);
         } else {
-          const size_t base = ((static_cast<size_t>(page) * 2 * kv_heads + kv) * page_tokens + key % page_tokens) * head_dim + d;
+          const size_t base = ((static_cast<size_t>(page) * planes * kv_heads + kv) * page_tokens + key % page_tokens) * head_dim + d;
           kval = to_float(cache[base]);
-          vval = to_float(cache[base + static_cast<size_t>(kv_heads) * page_tokens * head_dim]);
+          vval = planes == 2 ? to_float(cache[base + static_cast<size_t>(kv_heads) * page_tokens * head_dim]) : kval;
         }
       }
       sK[kk * (head_dim + 1) + d] = kval;
@@ -98,7 +106,9 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
       const float* krow = sK + c * (head_dim + 1);
       for (int d = 0; d < head_dim; ++d) dot = fmaf(qrow[d], krow[d], dot);
       visible[j] = row_valid && key <= my_pos && key >= my_first;
-      s[j] = visible[j] ? dot * scale : kMinusHuge;
+      dot *= scale;
+      if (softcap > 0.0f) dot = softcap * tanhf(dot / softcap);
+      s[j] = visible[j] ? dot : kMinusHuge;
       tile_max = fmaxf(tile_max, s[j]);
     }
 #pragma unroll
@@ -123,7 +133,7 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
 #pragma unroll
     for (int j = 0; j < DPT; ++j) {
       const int d = lane8 + 8 * j;
-      if (d < head_dim) {
+      if (d < value_dim) {
         float sum = 0.0f;
         for (int k = 0; k < kTileKeys; ++k) sum = fmaf(prow[k], sV[k * head_dim + d], sum);
         acc[j] = acc[j] * alpha + sum;
@@ -133,12 +143,15 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
 
   if (row_valid) {
     const float inv = 1.0f / l;
-    T* dst = out + (static_cast<size_t>(t0 + r) * heads + head) * head_dim;
-    const T* g = gate != nullptr ? gate + (t0 + r) * gate_stride + static_cast<long long>(head) * head_dim : nullptr;
+    T* dst = out + (static_cast<size_t>(t0 + r) * heads + head) * value_dim;
+    const T* g = gate != nullptr ? gate + (t0 + r) * gate_stride + static_cast<long long>(head) * (gate_per_head ? 1 : value_dim)
+                                 : nullptr;
+    const float whole = g != nullptr && gate_per_head ? sigmoid_of(to_float(g[0])) : 1.0f;
 #pragma unroll
     for (int j = 0; j < DPT; ++j) {
       const int d = lane8 + 8 * j;
-      if (d < head_dim) dst[d] = from_float<T>(acc[j] * inv * (g != nullptr ? sigmoid_of(to_float(g[d])) : 1.0f));
+      if (d < value_dim)
+        dst[d] = from_float<T>(acc[j] * inv * (g != nullptr && !gate_per_head ? sigmoid_of(to_float(g[d])) : whole));
     }
   }
 }
@@ -148,7 +161,8 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
                        int max_pages, const int* tile_request, const int* tile_start,
                        const int* tile_length, const int* positions, int tiles, int heads,
                        int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
-                       float scale, const void* gate, long long gate_stride, int* status, cudaStream_t stream) {
+                       float scale, const void* gate, long long gate_stride, int planes, int value_dim, float softcap,
+                       int gate_per_head, int* status, cudaStream_t stream) {
   const size_t shared = sizeof(float) * (static_cast<size_t>(kTileQueries) * head_dim +
                                          static_cast<size_t>(kTileKeys) * (head_dim + 1) +
                                          static_cast<size_t>(kTileKeys) * head_dim +
@@ -162,7 +176,8 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
   kernel<<<grid, kTileThreads, shared, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(cache), static_cast<T*>(out), block_tables,
       max_pages, tile_request, tile_start, tile_length, positions, heads, kv_heads, head_dim,
-      page_tokens, num_pages, window, chunk, scale, static_cast<const T*>(gate), gate_stride, status);
+      page_tokens, num_pages, window, chunk, scale, static_cast<const T*>(gate), gate_stride, planes, value_dim, softcap,
+      gate_per_head, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -179,17 +194,20 @@ MXB_API int mxb_paged_attention_tile(const void* q, const void* cache, void* out
                                      const int* tile_length, const int* positions, int tiles,
                                      int heads, int kv_heads, int head_dim, int page_tokens,
                                      int num_pages, int window, int chunk, float scale, int dtype, const void* gate,
-                                     long long gate_stride, int* status, cudaStream_t stream) {
+                                     long long gate_stride, int planes, int value_dim, float softcap,
+                                     int gate_per_head, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
-  if (head_dim <= 0 || head_dim > 256 || heads % kv_heads != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (head_dim <= 0 || head_dim > 576 || heads % kv_heads != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if ((planes != 1 && planes != 2) || value_dim <= 0 || value_dim > head_dim) return static_cast<int>(cudaErrorInvalidValue);
 #define ARGS q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length, positions, \
-             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, status, stream
+             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, planes, value_dim, softcap, gate_per_head, status, stream
 #define DISPATCH(T)                                           \
   if (head_dim <= 16) return launch_tile<T, 2>(ARGS);         \
   if (head_dim <= 32) return launch_tile<T, 4>(ARGS);         \
   if (head_dim <= 64) return launch_tile<T, 8>(ARGS);         \
   if (head_dim <= 128) return launch_tile<T, 16>(ARGS);       \
-  return launch_tile<T, 32>(ARGS);
+  if (head_dim <= 256) return launch_tile<T, 32>(ARGS);       \
+  return launch_tile<T, 72>(ARGS);
   if (dtype == kF32) { DISPATCH(float) }
   if (dtype == kBF16) { DISPATCH(__nv_bfloat16) }
 #undef DISPATCH

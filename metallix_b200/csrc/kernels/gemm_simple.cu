@@ -142,3 +142,30 @@ MXB_API int mxb_silu_mul(void* out, const void* gate_up, int dtype, long long to
     return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(cudaGetLastError());
 }
+
+namespace mxb {
+// out = max(x, 0)^2: the activation of a feed-forward without a gate, float32 inside.
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ out, const T* __restrict__ x, size_t count) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float v = fmaxf(to_float(x[i]), 0.0f);
+    out[i] = from_float<T>(v * v);
+  }
+}
+}  // namespace mxb
+
+MXB_API int mxb_relu_squared(void* out, const void* x, long long count, int dtype, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == mxb::kF32)
+    mxb::relu_squared_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<float*>(out), static_cast<const float*>(x), static_cast<size_t>(count));
+  else if (dtype == mxb::kBF16)
+    mxb::relu_squared_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x), static_cast<size_t>(count));
+  else
+    return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(cudaGetLastError());
+}

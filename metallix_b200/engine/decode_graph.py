@@ -259,7 +259,7 @@ class DecodeGraphs:
         gives the same logits, so nothing changes; a model with state of its
         own per request (which a replay would advance) gets one capture."""
         engine = self.engine
-        stateless = all(need is None or need.kind != "state" for need in engine.cache.needs)
+        stateless = not any(need is not None and need.has_state() for need in engine.cache.needs)
         tries = self.placements if stateless else 1
         first = self._capture(size, bound, pool=None)
         if tries <= 1:

@@ -116,7 +116,7 @@ class Engine:
         # up and captured on a live step, which therefore runs more than once:
         # harmless where a step only writes pages (written again with the
         # same values), not where a part keeps state that a step advances.
-        stateless = all(need is None or need.kind != "state" for need in self.cache.needs)
+        stateless = not any(need is not None and need.has_state() for need in self.cache.needs)
         self._step_graphs: Optional[Dict] = {} if self.graphs is not None and stateless else None
         self.replay_general_steps = True   # False: general steps are launched kernel by kernel (measurements)
         values = self.model.weight_bytes() / torch.empty((), dtype=self.dtype).element_size()

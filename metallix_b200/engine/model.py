@@ -8,6 +8,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config.spec import CacheNeed, ModelSpec
+from ..parts.block import open_streams, read_streams, sum_of_streams
 from ..parts.registry import (CacheView, Runtime, StepContext, WeightStore, _BUILDERS, build_part, settle)
 
 
@@ -68,6 +69,9 @@ class DecoderModel:
         ``[tokens, hidden]`` as that layer leaves it (the sums that otherwise
         ride along into the next layer's first kernel are made at once then)."""
         residual = self.embedding.forward(token_ids)
+        streams = self.spec.streams
+        if streams:   # several copies of the stream: [tokens, streams, hidden]
+            residual = open_streams(residual, streams)
         pending = None
         for index, run in enumerate(self.order):
             block = self.blocks[run.layer]
@@ -75,9 +79,12 @@ class DecoderModel:
             if tap is not None:
                 settle(residual, pending)
                 pending = None
-                tap(index, residual)
+                tap(index, sum_of_streams(residual) if streams else residual)
         if wanted_rows is None or wanted_rows.numel() == 0:
             return None
+        if streams:   # what is pending joins, the streams are summed and normed, on the wanted rows only
+            return self.head.forward(read_streams(residual, pending, None, self.final_norm, self.runtime.dtype,
+                                                  rows_index=wanted_rows, keep_streams=False))
         settle(residual, pending)
         normed = self.final_norm.forward(residual, self.runtime.dtype, rows_index=wanted_rows)
         return self.head.forward(normed)

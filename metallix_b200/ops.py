@@ -36,7 +36,16 @@ _SIGNATURES = {
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
                                _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                 _F, _I, _P, _L, _P, _P],
+                                 _F, _I, _P, _L, _I, _I, _F, _I, _P, _P],
+    "mxb_stream_mix": [_P, _P, _P, _L, _L, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+    "mxb_weighted_sum": [_P, _P, _P, _L, _L, _F, _F, _I, _I, _I, _P],
+    "mxb_mlstm_state_values": [_I, _I, _I],
+    "mxb_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _L, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                       _P, _P],
+    "mxb_head_norm_gate": [_P, _P, _P, _L, _I, _P, _I, _I, _I, _I, _F, _P],
+    "mxb_latent_cache": [_P, _L, _P, _F, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "mxb_rotate_into": [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P, _P],
+    "mxb_relu_squared": [_P, _P, _L, _I, _P],
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                                    _F, _I, _P, _L, _P, _P],
     "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
@@ -362,6 +371,203 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+# ------------------------------------- several residual streams, Dynamic Tanh
+MAX_STREAMS = 8
+
+
+def stream_mix(streams: torch.Tensor, result: Optional[torch.Tensor] = None,
+               channel_scale: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+               out_weights: Optional[torch.Tensor] = None, in_weights: Optional[torch.Tensor] = None,
+               alpha: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+               norm_bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+               rows_index: Optional[torch.Tensor] = None, read: bool = True, keep_streams: bool = True,
+               second: Optional[torch.Tensor] = None, weights=(1.0, 1.0)) -> Optional[torch.Tensor]:
+    """One pass over ``streams`` (float32 ``[tokens, s, width]``, in place).
+
+    With ``result`` ``[tokens, width]`` (rows may be strided): every stream t
+    becomes sum_s mix[s, t] x_s + out_weights[t] * (channel_scale * y), where
+    y = weights[0] * result (+ weights[1] * second). Then, with ``read``:
+    u = sum_s in_weights[s] x_s (the plain sum without ``in_weights``) and, with
+    ``alpha`` (a scalar tensor), Dynamic Tanh tanh(alpha u) * norm_weight +
+    norm_bias; returns that as ``[rows, width]`` in ``out_dtype``.
+    ``rows_index`` (int32): only those tokens are worked on.
+    ``keep_streams=False``: the new streams are not stored (a step's last read)."""
+    _check(streams, "streams", (torch.float32,), 3)
+    tokens, count, width = streams.shape
+    _need(1 <= count <= MAX_STREAMS, f"{count} residual streams; the kernel takes 1..{MAX_STREAMS}")
+    rows = tokens
+    if rows_index is not None:
+        _check(rows_index, "rows_index", (torch.int32,), 1)
+        rows = rows_index.numel()
+    result_code, lda, ldb = F32, 0, 0
+    if result is not None:
+        for name, tensor in (("result", result), ("second", second)):
+            if tensor is None:
+                continue
+            _need(tensor.is_cuda and tensor.dtype in _CODES and tensor.dim() == 2 and tensor.stride(1) == 1
+                  and tensor.shape == (tokens, width) and tensor.dtype == result.dtype,
+                  f"{name} must be a CUDA [tokens, width] tensor with unit column stride")
+        result_code, lda = _CODES[result.dtype], result.stride(0)
+        ldb = second.stride(0) if second is not None else 0
+        for name, tensor, size in (("mix", mix, count * count), ("out_weights", out_weights, count)):
+            _need(tensor is not None, f"{name} is needed to write a result back")
+            _check(tensor, name, (torch.float32,))
+            _need(tensor.numel() == size, f"{name} must have {size} values")
+    else:
+        _need(second is None, "a second result needs a first")
+    for name, tensor, size in (("channel_scale", channel_scale, width), ("in_weights", in_weights, count),
+                               ("alpha", alpha, 1), ("norm_weight", norm_weight, width), ("norm_bias", norm_bias, width)):
+        if tensor is not None:
+            _check(tensor, name, (torch.float32,))
+            _need(tensor.numel() == size, f"{name} must have {size} values")
+    out = None
+    if read:
+        _need(out_dtype in _CODES, "out_dtype must be float32 or bfloat16")
+        _need(alpha is None or norm_weight is not None, "Dynamic Tanh needs its weight")
+        out = torch.empty((rows, width), dtype=out_dtype, device=streams.device)
+    _call("mxb_stream_mix", streams.data_ptr(), _ptr(result), _ptr(second), lda, ldb, float(weights[0]),
+          float(weights[1]), result_code, _ptr(channel_scale), _ptr(mix), _ptr(out_weights), _ptr(in_weights),
+          _ptr(alpha), _ptr(norm_weight), _ptr(norm_bias), _ptr(out), _CODES[out_dtype] if out is not None else F32,
+          _ptr(rows_index), rows, width, count, 1 if keep_streams else 0, _stream())
+    return out
+
+
+def weighted_sum(x: torch.Tensor, y: torch.Tensor, a: float, b: float) -> torch.Tensor:
+    """a * x + b * y as float32 ``[rows, width]`` (rows of x and y may be strided)."""
+    for name, tensor in (("x", x), ("y", y)):
+        _need(tensor.is_cuda and tensor.dtype in _CODES and tensor.dim() == 2 and tensor.stride(1) == 1,
+              f"{name} must be a CUDA [rows, width] tensor with unit column stride")
+    _need(x.shape == y.shape and x.dtype == y.dtype, "x and y differ in shape or dtype")
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _call("mxb_weighted_sum", out.data_ptr(), x.data_ptr(), y.data_ptr(), x.stride(0), y.stride(0), float(a), float(b),
+          x.shape[0], x.shape[1], _CODES[x.dtype], _stream())
+    return out
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """max(x, 0)^2, float32 inside."""
+    _check(x, "x", tuple(_CODES))
+    out = torch.empty_like(x)
+    _call("mxb_relu_squared", out.data_ptr(), x.data_ptr(), x.numel(), _CODES[x.dtype], _stream())
+    return out
+
+
+# ------------------------------------------------------- matrix-memory recurrence
+def mlstm_state_values(heads: int, dim: int, vdim: int) -> int:
+    """float32 values one request's state of the recurrence takes."""
+    return int(_fn("mxb_mlstm_state_values")(heads, dim, vdim))
+
+
+def mlstm_scan(proj: torch.Tensor, offsets, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float,
+               state: torch.Tensor, row_start: torch.Tensor, row_length: torch.Tensor,
+               request_slots: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """The matrix-memory recurrence over a step's tokens. ``proj``
+    ``[tokens, columns]`` holds, from the column ``offsets`` (q, k, v, i, f)
+    on, heads * dim queries and keys, heads * vdim values and one input- and
+    one forget-gate pre-activation per head. Request row r brings
+    ``row_length[r]`` consecutive tokens from packed token ``row_start[r]`` on
+    (0: a padding row) and owns slot ``request_slots[r]`` of ``state``
+    (float32 ``[slots, mlstm_state_values]``, advanced in place). Returns
+    float32 ``[tokens, heads * vdim]``: each head's C^T q over its bounded
+    normaliser, before the head norm."""
+    _need(proj.is_cuda and proj.dtype in _CODES and proj.dim() == 2 and proj.stride(1) == 1,
+          "proj must be a CUDA [tokens, columns] tensor with unit column stride")
+    _check(state, "state", (torch.float32,), 2)
+    _need(state.shape[1] == mlstm_state_values(heads, dim, vdim), "state slots have the wrong size")
+    for name, tensor in (("row_start", row_start), ("row_length", row_length), ("request_slots", request_slots)):
+        _check(tensor, name, (torch.int32,), 1)
+    rows = row_start.numel()
+    _need(row_length.numel() == rows and request_slots.numel() >= rows, "row lists differ in length")
+    for name, tensor in (("i_bias", i_bias), ("f_bias", f_bias)):
+        _check(tensor, name, (torch.float32,), 1)
+        _need(tensor.numel() == heads, f"{name} must have one value per head")
+    q_off, k_off, v_off, i_off, f_off = (int(o) for o in offsets)
+    _need(max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim, i_off + heads, f_off + heads)
+          <= proj.shape[1], "the column offsets reach beyond proj")
+    _need(cap > 0.0, "the cap on the gates must be positive")
+    tokens = proj.shape[0]
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    _call("mxb_mlstm_scan", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, i_off, f_off, i_bias.data_ptr(),
+          f_bias.data_ptr(), float(cap), float(dim) ** -0.5, state.data_ptr(), state.stride(0), state.shape[0],
+          row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(), out.data_ptr(), rows, heads, dim,
+          vdim, _CODES[proj.dtype], status_word(proj.device).data_ptr(), _stream())
+    return out
+
+
+def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], heads: int, eps: float,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """Each head of x (float32 ``[tokens, heads * vdim]``) over its root mean
+    square, times ``weight`` (all heads' size), times sigmoid(gate) (same shape,
+    rows may be strided)."""
+    _check(x, "x", (torch.float32,), 2)
+    _check(weight, "weight", (torch.float32,), 1)
+    tokens, width = x.shape
+    _need(width % heads == 0 and weight.numel() == width, "x, weight and the heads do not fit")
+    gate_code, ldg = F32, 0
+    if gate is not None:
+        _need(gate.is_cuda and gate.dtype in _CODES and gate.dim() == 2 and gate.stride(1) == 1
+              and gate.shape == x.shape, "gate must be [tokens, heads * vdim] with unit column stride")
+        gate_code, ldg = _CODES[gate.dtype], gate.stride(0)
+    _need(out_dtype in _CODES, "out_dtype must be float32 or bfloat16")
+    out = torch.empty((tokens, width), dtype=out_dtype, device=x.device)
+    _call("mxb_head_norm_gate", x.data_ptr(), weight.data_ptr(), _ptr(gate), ldg, gate_code, out.data_ptr(),
+          _CODES[out_dtype], tokens, heads, width // heads, float(eps), _stream())
+    return out
+
+
+# ------------------------------------------------- attention through a latent
+def latent_cache(x: torch.Tensor, weight: torch.Tensor, eps: float, rank: int, cache: torch.Tensor,
+                 slots: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                 sin: Optional[torch.Tensor], interleaved: bool) -> None:
+    """x ``[tokens, rank + rot]`` (rows may be strided): the first ``rank``
+    values are RMS-normed with ``weight``, the rest rotated by the positions,
+    and both stored at ``slots`` of the one-plane pool
+    ``[pages, 1, 1, page_tokens, rank + rot]``."""
+    _need(x.is_cuda and x.dtype in _CODES and x.dim() == 2 and x.stride(1) == 1, "x must be [tokens, rank + rot]")
+    _check(cache, "cache", (x.dtype,), 5)
+    num_pages, planes, kv_heads, page_tokens, width = cache.shape
+    _need(planes == 1 and kv_heads == 1 and width == x.shape[1] and 0 < rank <= width,
+          "cache must be [pages, 1, 1, page_tokens, rank + rot]")
+    _check(weight, "weight", (torch.float32,), 1)
+    _need(weight.numel() == rank, "the latent's norm weight has the wrong size")
+    tokens = x.shape[0]
+    _check(slots, "slots", (torch.int32,), 1)
+    _check(positions, "positions", (torch.int32,), 1)
+    _need(slots.numel() == tokens and positions.numel() == tokens, "one slot and one position per token")
+    rotary_dim, table_positions = _tables(cos, sin, width - rank)
+    _call("mxb_latent_cache", x.data_ptr(), x.stride(0), weight.data_ptr(), float(eps), rank, width - rank, rotary_dim,
+          1 if interleaved else 0, _ptr(cos), _ptr(sin), table_positions, positions.data_ptr(), slots.data_ptr(),
+          cache.data_ptr(), page_tokens, num_pages, tokens, _CODES[x.dtype], status_word(x.device).data_ptr(),
+          _stream())
+
+
+def _tables(cos, sin, width: int):
+    if cos is None:
+        return 0, 0
+    _check(cos, "cos", (torch.float32,), 2)
+    _check(sin, "sin", (torch.float32,), 2)
+    _need(cos.shape == sin.shape and cos.shape[1] * 2 <= width, "cos and sin do not fit the rotated width")
+    return cos.shape[1] * 2, cos.shape[0]
+
+
+def rotate_into(src: torch.Tensor, src_off: int, src_step: int, dst: torch.Tensor, dst_off: int, rot: int,
+                positions: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                interleaved: bool) -> None:
+    """For every token and head: the ``rot`` values at
+    ``src[token, src_off + head * src_step ...]`` rotated by the token's
+    position into ``dst[token, head, dst_off ...]`` (dst ``[tokens, heads, step]``)."""
+    _need(src.is_cuda and src.dtype in _CODES and src.dim() == 2 and src.stride(1) == 1, "src must be [tokens, columns]")
+    _check(dst, "dst", (src.dtype,), 3)
+    tokens, heads, step = dst.shape
+    _need(src.shape[0] == tokens and src_off + (heads - 1) * src_step + rot <= src.shape[1] and dst_off + rot <= step,
+          "the rotated values do not fit src or dst")
+    _check(positions, "positions", (torch.int32,), 1)
+    rotary_dim, table_positions = _tables(cos, sin, rot)
+    _call("mxb_rotate_into", src.data_ptr(), src.stride(0), src_off, src_step, dst.data_ptr(), dst_off, step, heads, rot,
+          rotary_dim, 1 if interleaved else 0, _ptr(cos), _ptr(sin), table_positions, positions.data_ptr(), tokens,
+          _CODES[src.dtype], status_word(src.device).data_ptr(), _stream())
+
+
 # ------------------------------------------------------- copies in the cache
 def copy_units(pool: torch.Tensor, pairs: torch.Tensor) -> None:
     """pool[:, target] = pool[:, source] for every (source, target) row of
@@ -466,23 +672,32 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
                          block_tables: torch.Tensor, tile_request: torch.Tensor,
                          tile_start: torch.Tensor, tile_length: torch.Tensor,
                          positions: torch.Tensor, scale: float, window: int = 0, chunk: int = 0,
-                         gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                         gate_per_head: bool = False) -> torch.Tensor:
     """Attention of every query token over its request's cached keys (itself
-    included) in float32; q and out are [tokens, heads, head_dim]. ``window``:
+    included) in float32; q is [tokens, heads, head_dim], out
+    [tokens, heads, value_dim] with value_dim at most head_dim (the first
+    that many values of a value row). ``cache`` is
+    [pages, planes, kv_heads, page_tokens, head_dim]: two planes hold keys and
+    values, one plane holds rows that are keys and values at once. ``window``:
     only the last that many positions are seen; ``chunk``: only the keys of the
     query's own chunk of that many positions, counted from position 0;
-    ``gate`` ([tokens, heads * head_dim], rows may be strided): the output is
-    multiplied by sigmoid(gate) as it is written."""
+    ``softcap`` c: scores pass c tanh(s / c) ahead of the softmax;
+    ``gate`` ([tokens, heads * value_dim], or [tokens, heads] with
+    ``gate_per_head``; rows may be strided): the output is multiplied by
+    sigmoid(gate) as it is written."""
     dtype = q.dtype
     _check(q, "q", tuple(_CODES), 3)
     _check(out, "out", (dtype,), 3)
     _check(cache, "cache", (dtype,), 5)
-    _need(out.shape == q.shape, "out and q differ in shape")
     tokens, heads, head_dim = q.shape
-    num_pages, two, kv_heads, page_tokens, cache_dim = cache.shape
-    _need(two == 2 and cache_dim == head_dim, "cache must be [pages, 2, kv_heads, page_tokens, head_dim]")
+    num_pages, planes, kv_heads, page_tokens, cache_dim = cache.shape
+    _need(planes in (1, 2) and cache_dim == head_dim, "cache must be [pages, 1 or 2, kv_heads, page_tokens, head_dim]")
+    value_dim = out.shape[2]
+    _need(out.shape[:2] == q.shape[:2] and 0 < value_dim <= head_dim, "out must be [tokens, heads, value_dim <= head_dim]")
     _need(heads % kv_heads == 0, f"{heads} query heads cannot share {kv_heads} key/value heads")
-    _need(0 < head_dim <= 256, f"head_dim {head_dim} is outside 1..256")
+    _need(0 < head_dim <= 576, f"head_dim {head_dim} is outside 1..576")
+    _need(softcap >= 0.0, "the cap on the scores cannot be negative")
     _check(block_tables, "block_tables", (torch.int32,), 2)
     for name, tensor in (("tile_request", tile_request), ("tile_start", tile_start),
                          ("tile_length", tile_length), ("positions", positions)):
@@ -490,11 +705,18 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     tiles = tile_request.numel()
     _need(tile_start.numel() == tiles and tile_length.numel() == tiles, "tile lists differ in length")
     _need(positions.numel() == tokens, "one position per token")
+    if gate is not None and gate_per_head:
+        _need(gate.is_cuda and gate.dtype == dtype and gate.dim() == 2 and gate.stride(1) == 1
+              and gate.shape == (tokens, heads), "a per-head gate must be [tokens, heads] in q's type")
+        gate_stride = gate.stride(0)
+    else:
+        gate_stride = _gate_stride(gate, out)
     _call("mxb_paged_attention_tile", q.data_ptr(), cache.data_ptr(), out.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(),
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
           kv_heads, head_dim, page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[dtype],
-          _ptr(gate), _gate_stride(gate, q), status_word(q.device).data_ptr(), _stream())
+          _ptr(gate), gate_stride, planes, value_dim, float(softcap), 1 if gate_per_head else 0,
+          status_word(q.device).data_ptr(), _stream())
     return out
 
 

@@ -12,7 +12,12 @@ without a value projection reuses the key projection's raw output (ahead of
 its norm and rotation) as the values (no ``v_proj``); ``chunk`` lets a query
 reach back only to the last absolute multiple of that many positions;
 ``gate_proj`` multiplies the concatenated heads by sigmoid(a Wg^T) ahead of the
-output projection.
+output projection (``gate_scope="head"``: Wg has one row per head, and a
+head's whole output is multiplied by one number); ``softcap`` c bounds the
+scores, s <- c tanh(s / c), ahead of the softmax; ``value_dim`` lets the
+values be wider or narrower than the keys (a page then holds rows as wide as
+the wider of the two, the others padded with zeros). A score cap, a per-head
+gate or values of another width run on the general kernel only.
 
 Every size and constant is a parameter. When the head norms are RMSNorms (or
 absent) and the position encoding offers cos/sin tables (or is absent), norm,
@@ -105,6 +110,23 @@ def attention_tiles(plan: StepPlan) -> Prepared:
                              "longest_keys": longest_keys}, graph_key=many_keys)
 
 
+def tiles_of(ctx: StepContext) -> Dict[str, object]:
+    """The step's tile lists: what the engine prepared, or (for a caller
+    that built a context by hand) made here from the host lists."""
+    tiles = ctx.extras.get("attention_tiles")
+    if tiles is None:
+        if ctx.request_offsets is None:
+            raise ValueError("the attention's tile lists were not prepared for this step")
+        counts = [ctx.request_offsets[row + 1] - ctx.request_offsets[row] for row in range(ctx.num_requests)]
+        ends = [start + count for start, count in zip(ctx.request_positions, counts)]
+        prepared = attention_tiles(StepPlan(counts, ctx.request_positions, len(counts), max(ends)))
+        tiles = dict(prepared.facts)
+        for name, array in prepared.arrays.items():
+            tiles[name] = torch.from_numpy(array).to(ctx.device)
+        ctx.extras["attention_tiles"] = tiles
+    return tiles
+
+
 class GQAttention:
     kind = "gqa_attention"
     graph_safe = True  # launches the same kernels whatever the step's integers are
@@ -128,14 +150,27 @@ class GQAttention:
             raise ValueError(f"head_dim {self.head_dim}: the attention kernels take even sizes up to 256")
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
+        self.value_dim = spec.get("value_dim") or self.head_dim
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.gate_scope = spec.get("gate_scope") or "value"
+        if self.gate_scope not in ("value", "head"):
+            raise ValueError(f"gate_scope must be 'value' or 'head', got {self.gate_scope!r}")
+        if self.softcap < 0.0 or not 0 < self.value_dim <= 576:
+            raise ValueError(f"softcap {self.softcap} or value_dim {self.value_dim} out of range")
+        self.v_size = self.num_kv_heads * self.value_dim
+        self.out_size = self.num_heads * self.value_dim
+        self.row_dim = max(self.head_dim, self.value_dim)      # width of a cached row
         # v_proj absent: the key projection's raw output is the values too. gate_proj: an
         # output gate over the concatenated heads, from the mixer's own input.
         self.own_values = spec.get("v_proj") is not None
         self.gated = spec.get("gate_proj") is not None
         stacked = []
+        if not self.own_values and self.value_dim != self.head_dim:
+            raise ValueError("values taken from the key projection are as wide as the keys")
+        gate_rows = self.num_heads if self.gate_scope == "head" else self.out_size
         for name, rows, present in (("q_proj", self.q_size, True), ("k_proj", self.kv_size, True),
-                                    ("v_proj", self.kv_size, self.own_values),
-                                    ("gate_proj", self.q_size, self.gated)):
+                                    ("v_proj", self.v_size, self.own_values),
+                                    ("gate_proj", gate_rows, self.gated)):
             if not present:
                 continue
             weight = weights.take(spec[name])
@@ -144,9 +179,10 @@ class GQAttention:
             stacked.append(weight)
         # rows: all q heads, then k heads, then v heads (if any), then the gate (if any)
         self.qkv = Linear.stacked(stacked, runtime)
-        self.gate_offset = self.q_size + self.kv_size * (2 if self.own_values else 1)
+        self.gate_offset = self.q_size + self.kv_size + (self.v_size if self.own_values else 0)
+        self.gate_rows = gate_rows
         self.o = Linear(weights.take(spec["o_proj"]), runtime)
-        if (self.o.out_features, self.o.in_features) != (self.hidden_size, self.q_size):
+        if (self.o.out_features, self.o.in_features) != (self.hidden_size, self.out_size):
             raise ValueError(f"{spec['o_proj']} is {tuple(self.o.weight.shape)}")
         self.q_norm = build_part("norm", spec.get("q_norm"), weights, runtime)
         self.k_norm = build_part("norm", spec.get("k_norm"), weights, runtime)
@@ -159,35 +195,25 @@ class GQAttention:
         norms_fuse = all(n is None or isinstance(n, RMSNorm) for n in (self.q_norm, self.k_norm))
         eps_agree = (self.q_norm is None or self.k_norm is None or self.q_norm.eps == self.k_norm.eps)
         position_fuses = self.position is None or getattr(self.position, "fused_tables", False)
-        self.fused = norms_fuse and eps_agree and position_fuses
         self.dtype = runtime.dtype
-        self.split_decode = ops.decode_attention_supported(self.head_dim, self.num_heads,
-                                                           self.num_kv_heads, self.dtype)
-        self.flash = ops.flash_prefill_supported(self.head_dim, self.num_heads, self.num_kv_heads,
-                                                 self.dtype)
+        # What only the general kernel does: a cap on the scores, one gate per
+        # head, values of another width than the keys.
+        self.general_only = bool(self.softcap) or self.gate_scope == "head" or self.value_dim != self.head_dim
+        self.fused = norms_fuse and eps_agree and position_fuses and self.value_dim == self.head_dim
+        self.split_decode = not self.general_only and ops.decode_attention_supported(
+            self.head_dim, self.num_heads, self.num_kv_heads, self.dtype)
+        self.flash = not self.general_only and ops.flash_prefill_supported(
+            self.head_dim, self.num_heads, self.num_kv_heads, self.dtype)
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(kind="kv_pages", kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+        return CacheNeed(kind="kv_pages", kv_heads=self.num_kv_heads, head_dim=self.row_dim,
                          window=self.window or None, chunk=self.chunk or None)
 
     def parts(self):
         return [self.q_norm, self.k_norm, self.position]
 
     def _tiles(self, ctx: StepContext) -> Dict[str, object]:
-        """The step's tile lists: what the engine prepared, or (for a caller
-        that built a context by hand) made here from the host lists."""
-        tiles = ctx.extras.get(self.step_key)
-        if tiles is None:
-            if ctx.request_offsets is None:
-                raise ValueError("the attention's tile lists were not prepared for this step")
-            counts = [ctx.request_offsets[row + 1] - ctx.request_offsets[row] for row in range(ctx.num_requests)]
-            ends = [start + count for start, count in zip(ctx.request_positions, counts)]
-            prepared = attention_tiles(StepPlan(counts, ctx.request_positions, len(counts), max(ends)))
-            tiles = dict(prepared.facts)
-            for name, array in prepared.arrays.items():
-                tiles[name] = torch.from_numpy(array).to(ctx.device)
-            ctx.extras[self.step_key] = tiles
-        return tiles
+        return tiles_of(ctx)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         return self._attend(x, ctx, cache, summands=False)
@@ -204,9 +230,11 @@ class GQAttention:
         qkv = self.qkv.forward(x)
         q = qkv[:, :self.q_size]
         k = qkv[:, self.q_size:self.q_size + self.kv_size]
-        v = qkv[:, self.q_size + self.kv_size:self.q_size + 2 * self.kv_size] if self.own_values else k
-        gate = qkv[:, self.gate_offset:self.gate_offset + self.q_size] if self.gated else None
+        v = qkv[:, self.q_size + self.kv_size:self.q_size + self.kv_size + self.v_size] if self.own_values else k
+        gate = qkv[:, self.gate_offset:self.gate_offset + self.gate_rows] if self.gated else None
         per_head = self.norm_scope == "head"
+        if self.value_dim != self.head_dim:
+            return self._attend_unequal(x, q, k, v, gate, ctx, cache)
         q_heads = torch.empty((tokens, self.num_heads, self.head_dim), dtype=self.dtype, device=x.device)
         write = cache.write and cache.slots is not None
         if self.fused:
@@ -268,8 +296,45 @@ class GQAttention:
         if rest is not None and tiles["tile_request"][rest].numel():
             ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, tiles["tile_request"][rest],
                                      tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
-                                     self.scale, self.window, self.chunk, gate=gate)
+                                     self.scale, self.window, self.chunk, gate=gate, softcap=self.softcap,
+                                     gate_per_head=self.gate_scope == "head")
         return self.o.forward(out.view(tokens, self.q_size))
+
+    def _attend_unequal(self, x, q, k, v, gate, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        """Values wider or narrower than the keys: a cached row is as wide as
+        the wider of the two; queries, keys or values are padded with zeros up
+        to it, and the output keeps the first ``value_dim`` values."""
+        tokens, width = x.shape[0], self.row_dim
+        per_head = self.norm_scope == "head"
+        parts = []
+        for rows, norm, heads in ((q, self.q_norm, self.num_heads), (k, self.k_norm, self.num_kv_heads)):
+            weight = norm.weight if norm is not None else None
+            if norm is not None and not isinstance(norm, RMSNorm):
+                shape = (tokens * heads, self.head_dim) if per_head else (tokens, heads * self.head_dim)
+                rows = norm.forward(rows.reshape(shape).contiguous(), self.dtype).view(tokens, heads * self.head_dim)
+                weight = None
+            tables = self.position is not None and getattr(self.position, "fused_tables", False)
+            if self.position is not None and not tables:
+                raise ValueError("values of another width than the keys need a position part with cos/sin tables")
+            parts.append(ops.norm_rotate_heads(
+                rows, self.head_dim, ctx.positions, weight=weight, cos=self.position.cos if tables else None,
+                sin=self.position.sin if tables else None, eps=norm.eps if weight is not None else 0.0,
+                interleaved=bool(getattr(self.position, "interleaved", False)), norm_scope=self.norm_scope))
+        q_heads, k_heads = parts
+        pad = lambda t, have: torch.nn.functional.pad(t, (0, width - have)) if have < width else t
+        q_rows = pad(q_heads, self.head_dim).contiguous()
+        if cache.write and cache.slots is not None:
+            k_rows = pad(k_heads, self.head_dim).reshape(tokens, self.num_kv_heads * width)
+            v_rows = pad(v.reshape(tokens, self.num_kv_heads, self.value_dim), self.value_dim) \
+                .reshape(tokens, self.num_kv_heads * width)
+            ops.write_cache(k_rows, v_rows, cache.pool, cache.slots, ctx.positions)
+        tiles = tiles_of(ctx)
+        out = torch.empty((tokens, self.num_heads, self.value_dim), dtype=self.dtype, device=x.device)
+        ops.paged_attention_tile(q_rows, cache.pool, out, cache.block_tables, tiles["tile_request"],
+                                 tiles["tile_start"], tiles["tile_length"], ctx.positions, self.scale, self.window,
+                                 self.chunk, gate=gate, softcap=self.softcap,
+                                 gate_per_head=self.gate_scope == "head")
+        return self.o.forward(out.view(tokens, self.out_size))
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()

@@ -12,6 +12,13 @@ r = x + post1(mixer(norm1(x))); x' = r + post2(feed_forward(norm2(r))), the
 feed-forward half being optional. What a sublayer leaves is handed on with
 the norm it still has to pass (``Pending``), so that this norm, the residual
 sum and the next sublayer's norm run as one kernel.
+
+``hyper_connections`` keeps s copies x_1 .. x_s of the residual stream
+(``[tokens, s, hidden]``, float32). Sublayer q reads u = sum_s in_q[s] x_s,
+runs on norm(u), and its result y, times a per-channel layer scale, goes back
+to all streams at once: x_t <- sum_s mix_q[s, t] x_s + out_q[t] y. What a
+sublayer leaves is handed on as a ``StreamWrite``; the write, the next read
+and (when it is elementwise) the next norm are one kernel.
 """
 from __future__ import annotations
 
@@ -20,7 +27,10 @@ from typing import Optional
 import torch
 
 from ..config.spec import LayerSpec
-from .registry import CacheView, Pending, Runtime, StepContext, WeightStore, build_part, register_part
+from dataclasses import dataclass
+
+from .. import ops
+from .registry import CacheView, Pending, Runtime, StepContext, WeightStore, build_part, register_part, settle
 
 
 class PreNormResidualBlock:
@@ -96,3 +106,102 @@ register_part("block", "sandwich_residual",
               lambda layer, weights, runtime: SandwichNormBlock(layer, weights, runtime))
 register_part("block", "prenorm_residual",
               lambda layer, weights, runtime: PreNormResidualBlock(layer, weights, runtime))
+
+
+@dataclass
+class StreamWrite:
+    """A sublayer's result on its way into several residual streams."""
+
+    result: torch.Tensor                    # [tokens, hidden]
+    channel_scale: Optional[torch.Tensor]   # [hidden] or None
+    mix: torch.Tensor                       # [s, s], indexed [from, to]
+    out_weights: torch.Tensor               # [s]
+
+    def settle(self, streams: torch.Tensor) -> None:
+        ops.stream_mix(streams, result=self.result, channel_scale=self.channel_scale, mix=self.mix,
+                       out_weights=self.out_weights, read=False)
+
+
+def read_streams(streams: torch.Tensor, pending, in_weights: Optional[torch.Tensor], norm, out_dtype: torch.dtype,
+                 rows_index: Optional[torch.Tensor] = None, keep_streams: bool = True) -> torch.Tensor:
+    """norm(sum_s in_weights[s] x_s) (the plain sum without ``in_weights``)
+    after ``pending`` has joined the streams, in one kernel where the norm is
+    elementwise and the pending result a ``StreamWrite``."""
+    if pending is not None and not isinstance(pending, StreamWrite):
+        settle(streams, pending)
+        pending = None
+    write = dict(result=pending.result, channel_scale=pending.channel_scale, mix=pending.mix,
+                 out_weights=pending.out_weights) if pending is not None else {}
+    if getattr(norm, "elementwise", False) and getattr(norm, "kind", None) == "dynamic_tanh":
+        return ops.stream_mix(streams, in_weights=in_weights, alpha=norm.alpha, norm_weight=norm.weight,
+                              norm_bias=norm.bias, out_dtype=out_dtype, rows_index=rows_index,
+                              keep_streams=keep_streams, **write)
+    mixed = ops.stream_mix(streams, in_weights=in_weights, out_dtype=torch.float32, rows_index=rows_index,
+                           keep_streams=keep_streams, **write)
+    return norm.forward(mixed, out_dtype) if norm is not None else mixed.to(out_dtype)
+
+
+def open_streams(embedded: torch.Tensor, count: int) -> torch.Tensor:
+    """``count`` copies of the embedding output side by side: [tokens, count, hidden]."""
+    return embedded.unsqueeze(1).expand(-1, count, -1).contiguous()
+
+
+def sum_of_streams(streams: torch.Tensor) -> torch.Tensor:
+    """[tokens, hidden]: what the streams add up to (float32)."""
+    return ops.stream_mix(streams, out_dtype=torch.float32)
+
+
+class HyperConnectionBlock:
+    kind = "hyper_connections"
+
+    def __init__(self, layer: LayerSpec, weights: WeightStore, runtime: Runtime):
+        self.name = layer.name
+        params = layer.block
+        self.streams = int(params["streams"])
+        if not 1 <= self.streams <= ops.MAX_STREAMS:
+            raise ValueError(f"{layer.name}: {self.streams} residual streams; 1..{ops.MAX_STREAMS} are taken")
+        self.mixer_norm = build_part("norm", layer.mixer_norm, weights, runtime)
+        self.mixer = build_part("mixer", layer.mixer, weights, runtime)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, runtime)
+        self.feed_forward_norm = None
+        if self.feed_forward is not None:
+            if layer.feed_forward_norm is None:
+                raise ValueError(f"{layer.name}: a feed-forward needs its norm")
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm, weights, runtime)
+        self.dtype = runtime.dtype
+        s = self.streams
+
+        def small(name, shape):
+            tensor = weights.take(name)
+            if tuple(tensor.shape) != shape:
+                raise ValueError(f"{name} is {tuple(tensor.shape)}, expected {shape}")
+            return tensor.to(device=runtime.device, dtype=torch.float32).contiguous()
+
+        def sublayer(prefix):
+            names = params[prefix]
+            scale = names.get("scale")
+            return {"in": small(names["in"], (s,)), "out": small(names["out"], (s,)),
+                    "mix": small(names["mix"], (s, s)),
+                    "scale": small(scale, (params["hidden_size"],)) if scale else None}
+
+        self.mixer_streams = sublayer("mixer")
+        self.feed_forward_streams = sublayer("feed_forward") if self.feed_forward is not None else None
+
+    def parts(self):
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def forward(self, streams: torch.Tensor, pending, ctx: StepContext, cache: CacheView):
+        """``streams`` (float32 [tokens, s, hidden], updated in place) with
+        ``pending`` still to join; returns the last sublayer's ``StreamWrite``."""
+        own = self.mixer_streams
+        mixer_in = read_streams(streams, pending, own["in"], self.mixer_norm, self.dtype)
+        left = StreamWrite(self.mixer.forward(mixer_in, ctx, cache), own["scale"], own["mix"], own["out"])
+        if self.feed_forward is None:
+            return left
+        own = self.feed_forward_streams
+        feed_in = read_streams(streams, left, own["in"], self.feed_forward_norm, self.dtype)
+        return StreamWrite(self.feed_forward.forward(feed_in, ctx), own["scale"], own["mix"], own["out"])
+
+
+register_part("block", "hyper_connections",
+              lambda layer, weights, runtime: HyperConnectionBlock(layer, weights, runtime))

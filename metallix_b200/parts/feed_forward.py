@@ -1,7 +1,10 @@
 """SwiGLU feed-forward: d = ((sigmoid(g) * g) * u) Wd^T with g = m Wg^T and
 u = m Wu^T (crates/models/qwen/src/forward.rs:1904-1920). Gate and up weights
 are stacked so that one product yields both; SiLU and the product with u are
-float32 inside the kernel."""
+float32 inside the kernel.
+
+``dense_ff`` is the feed-forward without a gate: d = act(m Wu^T) Wd^T, the
+activation a parameter (``relu_squared``: max(z, 0)^2)."""
 from __future__ import annotations
 
 import torch
@@ -54,3 +57,29 @@ class SwiGLU:
 
 
 register_part("feed_forward", "swiglu", lambda spec, weights, runtime: SwiGLU(spec, weights, runtime))
+
+
+class DenseFeedForward:
+    kind = "dense_ff"
+    ACTIVATIONS = {"relu_squared": ops.relu_squared}
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        hidden, inter = spec["hidden_size"], spec["intermediate_size"]
+        up, down = weights.take(spec["up_proj"]), weights.take(spec["down_proj"])
+        for name, weight, shape in (("up_proj", up, (inter, hidden)), ("down_proj", down, (hidden, inter))):
+            if tuple(weight.shape) != shape:
+                raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {shape}")
+        if spec["activation"] not in self.ACTIVATIONS:
+            raise ValueError(f"activation {spec['activation']!r}; one of {sorted(self.ACTIVATIONS)}")
+        self.activation = self.ACTIVATIONS[spec["activation"]]
+        self.up, self.down = Linear(up, runtime), Linear(down, runtime)
+        self.intermediate_size = inter
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return self.down.forward(self.activation(self.up.forward(x)))
+
+    def weight_bytes(self) -> int:
+        return self.up.weight_bytes() + self.down.weight_bytes()
+
+
+register_part("feed_forward", "dense_ff", lambda spec, weights, runtime: DenseFeedForward(spec, weights, runtime))

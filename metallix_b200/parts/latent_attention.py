@@ -1,0 +1,111 @@
+"""Attention whose keys and values come from one small latent per position.
+
+With H heads, per head D unrotated and R rotated query/key values, value
+width V, latent width r (and a query latent of width rq):
+
+    cq = RMSNorm(a Wdq^T),  q = cq Wuq^T          per head [D unrotated | R rotated]
+    a Wdkv^T = [z (r values) | kr (R values)],  c = RMSNorm(z)
+    head h:  k_h = Wuk_h c,  v_h = Wuv_h c
+    score = (q_u . k_h + rot(q_r) . rot(kr)) * scale,  causal softmax,  out = concat_h(sum_j p_j v_h,j) Wo^T
+
+Only c and rot(kr) are cached: one row of r + R values per position, shared
+by all heads (a pool of one plane and one key/value head). The up-projections
+are moved to the query's side, which is the same arithmetic in another order:
+q_u . (Wuk_h c) = (Wuk_h^T q_u) . c, and sum_j p_j Wuv_h c_j = Wuv_h (sum_j p_j c_j).
+So a head's query against the cache is [Wuk_h^T q_u | rot(q_r)] (r + R values),
+its output a mixture of latents (r values) that Wuv_h widens to V afterwards:
+attention with H query heads over one shared key/value head, whatever the
+context's length.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.spec import CacheNeed, PartSpec
+from .attention import attention_tiles, tiles_of
+from .linear import Linear
+from .registry import CacheView, Runtime, StepContext, WeightStore, build_part, register_part
+
+
+class LatentAttention:
+    kind = "latent_attention"
+    graph_safe = True
+    step_key = "attention_tiles"
+    prepare_step = staticmethod(attention_tiles)
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        hidden = spec["hidden_size"]
+        self.heads, self.dim, self.rot = spec["num_heads"], spec["head_dim"], spec["rotary_head_dim"]
+        self.vdim, self.rank, self.q_rank = spec["value_dim"], spec["kv_rank"], spec["q_rank"]
+        self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
+        self.width = self.rank + self.rot           # what a position's cache row holds
+        if not 0 < self.width <= 576:
+            raise ValueError(f"latent plus rotated key is {self.width} values wide; the kernel takes up to 576")
+        H, D, R, V = self.heads, self.dim, self.rot, self.vdim
+
+        def matrix(name, shape):
+            weight = weights.take(spec[name])
+            if tuple(weight.shape) != shape:
+                raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {shape}")
+            return weight
+
+        self.dq = Linear(matrix("q_down_proj", (self.q_rank, hidden)), runtime)
+        self.uq = Linear(matrix("q_up_proj", (H * (D + R), self.q_rank)), runtime)
+        self.dkv = Linear(matrix("kv_down_proj", (self.width, hidden)), runtime)
+        self.q_norm = build_part("norm", spec["q_norm"], weights, runtime)
+        self.kv_norm = build_part("norm", spec["kv_norm"], weights, runtime)
+        on_device = lambda t: t.to(device=runtime.device, dtype=runtime.dtype).contiguous()
+        uk = on_device(matrix("k_up_proj", (H * D, self.rank))).view(H, D, self.rank)
+        self.uk = uk                                            # [H, D, r]: q_u @ uk[h] -> latent side
+        self.uk_t = uk.transpose(1, 2).contiguous() if runtime.dtype == torch.float32 else None   # [H, r, D]
+        self.uv = on_device(matrix("v_up_proj", (H * V, self.rank))).view(H, V, self.rank)
+        self.o = Linear(matrix("o_proj", (hidden, H * V)), runtime)
+        self.position = build_part("position", spec.get("position"), weights, runtime)
+        self.dtype = runtime.dtype
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="kv_pages", kv_heads=1, head_dim=self.width, planes=1)
+
+    def parts(self):
+        return [self.q_norm, self.kv_norm, self.position]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        tokens, H, D, R, V, r = x.shape[0], self.heads, self.dim, self.rot, self.vdim, self.rank
+        cos = self.position.cos if self.position is not None else None
+        sin = self.position.sin if self.position is not None else None
+        paired = bool(getattr(self.position, "interleaved", False))
+        # the position's cache row: normed latent, rotated shared key part
+        if cache.write and cache.slots is not None:
+            ops.latent_cache(self.dkv.forward(x), self.kv_norm.weight, self.kv_norm.eps, r, cache.pool, cache.slots,
+                             ctx.positions, cos, sin, paired)
+        # queries: through their own latent, then onto the cache's side
+        q = self.uq.forward(self.q_norm.forward(self.dq.forward(x), self.dtype))       # [tokens, H * (D + R)]
+        q_heads = q.view(tokens, H, D + R)
+        q_cache = torch.empty((tokens, H, self.width), dtype=self.dtype, device=x.device)
+        if self.dtype == torch.float32:
+            for h in range(H):
+                ops.gemm_simple(q_heads[:, h, :D], self.uk_t[h], out=q_cache[:, h, :r])
+        else:
+            q_cache[:, :, :r].copy_(torch.bmm(q_heads[:, :, :D].transpose(0, 1), self.uk).transpose(0, 1))
+        ops.rotate_into(q, D, D + R, q_cache, r, R, ctx.positions, cos, sin, paired)
+        tiles = tiles_of(ctx)
+        mixed = torch.empty((tokens, H, r), dtype=self.dtype, device=x.device)
+        ops.paged_attention_tile(q_cache, cache.pool, mixed, cache.block_tables, tiles["tile_request"],
+                                 tiles["tile_start"], tiles["tile_length"], ctx.positions, self.scale)
+        # latents back to values, head by head
+        if self.dtype == torch.float32:
+            values = torch.empty((tokens, H * V), dtype=self.dtype, device=x.device)
+            for h in range(H):
+                ops.gemm_simple(mixed[:, h, :], self.uv[h], out=values[:, h * V:(h + 1) * V])
+        else:
+            values = torch.bmm(mixed.transpose(0, 1), self.uv.transpose(1, 2)).transpose(0, 1).reshape(tokens, H * V)
+        return self.o.forward(values)
+
+    def weight_bytes(self) -> int:
+        element = self.uk.element_size()
+        return (self.dq.weight_bytes() + self.uq.weight_bytes() + self.dkv.weight_bytes() + self.o.weight_bytes()
+                + (self.uk.numel() + self.uv.numel()) * element)
+
+
+register_part("mixer", "latent_attention", lambda spec, weights, runtime: LatentAttention(spec, weights, runtime))

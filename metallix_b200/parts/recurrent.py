@@ -1,0 +1,118 @@
+"""The matrix-memory recurrence (mLSTM) as a mixer with its state in the
+cache's request slots.
+
+Per head, with key width D and value width V, a request carries a matrix
+C [D, V], a vector n [D] and a running maximum m (all float32, all zero at
+the start of a sequence; m starts at 0, not at minus infinity). A token with
+input a brings q = a Wq^T D^-1/2, k = a Wk^T, v = a Wv^T and, with a cap c,
+
+    i = c tanh((a Wi^T + bi) / c)             log of the input gate
+    f = logsigmoid(c tanh((a Wf^T + bf) / c)) log of the forget gate
+    m' = max(f + m, i)
+    C' = exp(f + m - m') C + exp(i - m') k v^T,   n' likewise with k alone
+    o  = C'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
+
+Each head's o is divided by its root mean square, the heads side by side are
+multiplied by a weight and by sigmoid(a Wg^T), and projected by Wo. The six
+projections are one product whose output stays float32, since the gates, the
+state and everything that meets them are float32 in both precisions.
+
+A step's tokens of one request are walked in order by one kernel, whether the
+step brings one token or a portion of a prompt; what is carried between steps
+is the exact state, so a position's output does not depend on how the prompt
+was cut.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..config.spec import CacheNeed, PartSpec
+from .linear import Linear
+from .registry import CacheView, Prepared, Runtime, StepContext, StepPlan, WeightStore, register_part
+
+
+def request_rows(plan: StepPlan) -> Prepared:
+    """Where each request row's tokens lie in the packed step: ``row_start``
+    and ``row_length`` (0 for a padding row, which owns no state)."""
+    counts = np.asarray(plan.counts, dtype=np.int64)
+    starts = np.zeros(len(counts), dtype=np.int64)
+    np.cumsum(counts[:-1], out=starts[1:])
+    lengths = np.where(np.arange(len(counts)) < plan.live, counts, 0)
+    return Prepared({"row_start": starts.astype(np.int32), "row_length": lengths.astype(np.int32)}, {}, graph_key=None)
+
+
+class MatrixMemory:
+    kind = "mlstm"
+    graph_safe = True
+    step_key = "request_rows"
+    prepare_step = staticmethod(request_rows)
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        hidden = spec["hidden_size"]
+        self.heads, self.dim, self.vdim = spec["num_heads"], spec["head_dim"], spec["value_dim"]
+        self.cap, self.eps = float(spec["gate_cap"]), float(spec["eps"])
+        if self.cap <= 0.0:
+            raise ValueError(f"gate_cap must be positive, got {self.cap}")
+        k_size, v_size = self.heads * self.dim, self.heads * self.vdim
+        stacked, self.offsets, cursor = [], {}, 0
+        for name, rows in (("q_proj", k_size), ("k_proj", k_size), ("v_proj", v_size), ("gate_proj", v_size),
+                           ("input_gate_proj", self.heads), ("forget_gate_proj", self.heads)):
+            weight = weights.take(spec[name])
+            if tuple(weight.shape) != (rows, hidden):
+                raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {(rows, hidden)}")
+            stacked.append(weight)
+            self.offsets[name] = cursor
+            cursor += rows
+        self.inputs = Linear.stacked(stacked, runtime)   # rows: q, k, v, output gate, input gate, forget gate
+        as_float = lambda name, size: self._vector(weights.take(spec[name]), size, spec[name], runtime)
+        self.input_bias = as_float("input_gate_bias", self.heads)
+        self.forget_bias = as_float("forget_gate_bias", self.heads)
+        self.norm_weight = as_float("norm", v_size)
+        self.o = Linear(weights.take(spec["o_proj"]), runtime)
+        if (self.o.out_features, self.o.in_features) != (hidden, v_size):
+            raise ValueError(f"{spec['o_proj']} is {tuple(self.o.weight.shape)}")
+        self.dtype = runtime.dtype
+        self.state_values = self.heads * (self.dim * self.vdim + (-(-self.vdim // 32)) * (self.dim + 1))
+
+    @staticmethod
+    def _vector(tensor: torch.Tensor, size: int, name: str, runtime: Runtime) -> torch.Tensor:
+        if tensor.numel() != size:
+            raise ValueError(f"{name} has {tensor.numel()} values, expected {size}")
+        return tensor.to(device=runtime.device, dtype=torch.float32).reshape(-1).contiguous()
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="state", state_shape=(self.state_values,), state_dtype="float32")
+
+    def _rows(self, ctx: StepContext) -> Dict[str, torch.Tensor]:
+        rows = ctx.extras.get(self.step_key)
+        if rows is None:
+            if ctx.request_offsets is None:
+                raise ValueError("the recurrence's request rows were not prepared for this step")
+            counts = [ctx.request_offsets[row + 1] - ctx.request_offsets[row] for row in range(ctx.num_requests)]
+            prepared = request_rows(StepPlan(counts, ctx.request_positions, len(counts), 0))
+            rows = {name: torch.from_numpy(array).to(ctx.device) for name, array in prepared.arrays.items()}
+            ctx.extras[self.step_key] = rows
+        return rows
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        if cache.state is None:
+            raise ValueError("the matrix-memory mixer needs a state entry of the cache")
+        rows = self._rows(ctx)
+        proj = self.inputs.forward(x, out_dtype=torch.float32)
+        at = self.offsets
+        memory = ops.mlstm_scan(proj, (at["q_proj"], at["k_proj"], at["v_proj"], at["input_gate_proj"],
+                                       at["forget_gate_proj"]), self.input_bias, self.forget_bias, self.cap,
+                                cache.state, rows["row_start"], rows["row_length"], ctx.request_slots,
+                                self.heads, self.dim, self.vdim)
+        gate = proj[:, at["gate_proj"]:at["gate_proj"] + self.heads * self.vdim]
+        return self.o.forward(ops.head_norm_gate(memory, self.norm_weight, gate, self.heads, self.eps, self.dtype))
+
+    def weight_bytes(self) -> int:
+        return self.inputs.weight_bytes() + self.o.weight_bytes()
+
+
+register_part("mixer", "mlstm", lambda spec, weights, runtime: MatrixMemory(spec, weights, runtime))

@@ -102,6 +102,7 @@ class CacheView:
     slots: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None
     write: bool = True
+    members: Sequence["CacheView"] = ()
 
 
 @dataclass
@@ -121,7 +122,9 @@ def settle(residual: torch.Tensor, pending) -> None:
     from .. import ops
     if pending is None:
         return
-    if isinstance(pending, Pending):
+    if hasattr(pending, "settle"):      # a block arrangement's own way of joining the stream(s)
+        pending.settle(residual)
+    elif isinstance(pending, Pending):
         pending.norm.add_normed(residual, pending.delta)
     else:
         ops.add_(residual, pending)

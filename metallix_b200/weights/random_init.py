@@ -147,10 +147,13 @@ def random_tensors(config, seed: int, dtype: str = "bfloat16", device: str = "cp
     vector_dtype = _DTYPES[norm_dtype or dtype]
     tensors: Dict[str, torch.Tensor] = {}
     for name, shape in config.tensor_shapes().items():
-        norm = config.norm_tensor(name)   # False, True / "one" (a factor near 1) or "zero" (stored as factor - 1)
+        # False, True / "one" (a factor near 1), "zero" (stored as factor - 1) or "identity"
+        norm = config.norm_tensor(name)
         value = random_tensor(seed, name, shape, bool(norm), device)
         if norm == "zero":
             value = value - 1.0
+        elif norm == "identity":     # a small square matrix: the identity plus U(-0.1, 0.1)
+            value = value - 1.0 + torch.eye(shape[0], shape[1], dtype=value.dtype, device=value.device)
         tensors[name] = value.to(vector_dtype if norm else matrix_dtype)
     return tensors
 
