@@ -1,0 +1,694 @@
+"""The Zitezen decoder in the engine against the plain implementation
+(``plain_zitezen.py``): its configuration and mechanisms one at a time, then
+whole prompts layer by layer, decoding through the cache and the state,
+portions, mixed batches, pages and slots that come back, far keys and page
+borders, the first tokens, long decoding, generation through the scheduler
+and the trace program. Every model here is tiny, made for the test with random
+weights, and differs from layer to layer."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_zitezen as plain
+import replay_helpers as cuts
+from conftest import ROOT, random_ids
+
+
+# ------------------------------------------------------------ configurations
+def memory(heads, dim, vdim, cap):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}
+
+
+def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, base):
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+            "scale": scale, "rot": {"base": base, "dims": rot_dim}}
+
+
+def grouped(heads, kv_heads, dim, vdim, scale, softcap, rot):
+    out = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "rot": rot}
+    if softcap:
+        out["softcap"] = softcap
+    return out
+
+
+def layer(kind, mixer, ff):
+    return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def beside(left, right, left_scale, right_scale):
+    return {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale}
+
+
+# SMALL: three streams, a looped stretch that runs three times, sizes that are
+# no power of two, values wider than keys in the attention beside the
+# recurrence (24 against 16), a recurrence whose values take two slices of
+# columns with a remainder (40), two query heads per key/value head.
+SMALL = {"architecture": "Zitezen", "vocab": 211, "width": 72, "streams": 3, "norm": {"eps": 1e-6},
+         "loop": {"start": 1, "stop": 3, "times": 3},
+         "layers": [
+             layer("mlstm", memory(3, 8, 20, 8.0), 0),
+             layer("latent_attention", latent(4, 12, 6, 10, 20, 24, 0.3, 100.0), 56),
+             layer("parallel", beside(grouped(4, 2, 16, 24, 0.25, 5.0, {"base": 1.0e4, "dims": 8}),
+                                      memory(2, 12, 40, 10.0), 0.7, 1.2), 0),
+             layer("mlstm", memory(2, 20, 12, 14.0), 40)]}
+# WIDE: one stream, no loop, heads of 64 values with values as wide as keys
+# (norm, rotation and cache write as one kernel) and the whole head rotated,
+# a latent wider than a key tile row of the other layers.
+WIDE = {"architecture": "Zitezen", "vocab": 300, "width": 128, "streams": 1, "norm": {"eps": 1e-5},
+        "layers": [
+            layer("parallel", beside(grouped(6, 6, 64, 64, 0.11, 30.0, {"base": 1.0e5, "dims": 64}),
+                                     memory(2, 64, 64, 15.0), 1.0, 0.5), 160),
+            layer("latent_attention", latent(2, 32, 16, 64, 48, 32, 0.12, 1.0e4), 0),
+            layer("mlstm", memory(4, 32, 32, 12.0), 96)]}
+# BARE: the switches' other position: no cap on the scores, one key/value head
+# for all query heads, values narrower than keys (8 against 32), one pair
+# rotated, no rotation at all, a loop that runs once.
+BARE = {"architecture": "Zitezen", "vocab": 97, "width": 48, "streams": 2, "norm": {"eps": 1e-5},
+        "loop": {"start": 0, "stop": 2, "times": 1},
+        "layers": [
+            layer("parallel", beside(grouped(4, 1, 32, 8, 0.2, 0.0, {"base": 50.0, "dims": 2}),
+                                     memory(1, 16, 33, 6.0), -0.5, 1.0), 64),
+            layer("parallel", beside(grouped(2, 2, 8, 8, 0.4, 2.0, None), memory(3, 4, 4, 9.0), 1.0, 1.0), 0),
+            layer("latent_attention", latent(3, 8, 4, 6, 12, 10, 0.35, 30.0), 40)]}
+MODELS = {"small": (SMALL, 21, 8, 1.0), "wide": (WIDE, 22, 16, 1.0), "bare": (BARE, 23, 4, 1.0),
+          # query/key norm weights three times as large: scores nine times as far apart, so that which keys a
+          # query sees decides its output (float32 only, a bound of its own)
+          "sharp": (SMALL, 24, 8, 3.0)}
+CASES = [(name, dtype) for name in MODELS for dtype in ("float32", "bfloat16") if (name, dtype) != ("sharp", "bfloat16")]
+TOL = {"float32": 1e-4, "bfloat16": 2.5e-1}
+TOL_SHARP = 1e-3
+
+
+def bound(name, dtype):
+    return TOL_SHARP if name == "sharp" else TOL[dtype]
+
+
+def judge(name, dtype, seen, reference):
+    """Whether the logits a replay has seen are the plain side's. float32:
+    every position within the bound. bfloat16: the recurrence's quotient
+    magnifies rounding at the few positions where n . q passes through zero
+    (whole prompts show the same there), so the bound holds for 19 positions
+    out of 20, the median lies well inside it, and no position is off by the
+    size of a logit, which is what a lost state or a wrong key would do."""
+    errors = np.asarray([float(np.abs(row - reference[key][at]).max()) for (key, at), row in seen.items()])
+    assert len(errors)
+    if dtype == "float32":
+        assert errors.max() < bound(name, dtype), errors.max()
+    else:
+        assert np.median(errors) < 0.4 * TOL[dtype] and np.quantile(errors, 0.95) < TOL[dtype] and errors.max() < 1.0, \
+            (np.median(errors), np.quantile(errors, 0.95), errors.max())
+
+
+def write_folder(folder, raw, seed, sharpen):
+    """config.json + model.safetensors: bfloat16 matrices, float32 vectors (so
+    that the engine and the plain side hold the same values); projections
+    larger than the generator's (0.02) so that gates, scores and the state move."""
+    from metallix_b200.config import ZitezenConfig
+    from metallix_b200.weights import random_tensors
+    from metallix_b200.weights.safetensors_io import write_file
+    config = ZitezenConfig.from_dict(raw)
+    tensors = random_tensors(config, seed, dtype="bfloat16", norm_dtype="float32")
+    for name, value in tensors.items():
+        if value.dim() == 2 and ".hc" not in name:
+            # gate projections stay moderate: a large input gate drives the running maximum up and the
+            # normaliser's floor exp(-m) down, and where n . q crosses zero the quotient then magnifies
+            # whatever rounding the 16-bit products carry (the kernel's own test does reach the caps)
+            factor = 8.0 if name in ("head", "embed") else 2.0 if name.endswith((".i", ".f")) else 4.0
+            tensors[name] = (value.float() * factor).to(torch.bfloat16)
+        if name.endswith((".q.norm", ".k.norm", ".dq.norm")):
+            tensors[name] = value * sharpen
+        if name.endswith(".f.b"):
+            tensors[name] = value + 2.0     # forget gates near one: the state reaches far back
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as handle:
+        json.dump(config.to_dict(), handle)
+    write_file(os.path.join(folder, "model.safetensors"), {k: v.cpu() for k, v in tensors.items()},
+               order=list(config.tensor_shapes()))
+    return folder
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    """name -> (folder, config dict, tensors as float64 numpy, page size)."""
+    out = {}
+    for name, (raw, seed, page, sharpen) in MODELS.items():
+        folder = write_folder(str(tmp_path_factory.mktemp(f"zitezen_{name}")), raw, seed, sharpen)
+        config, tensors = plain.read_model(folder)
+        out[name] = (folder, config, tensors, page)
+    return out
+
+
+def make_engine(folders, name, dtype, pages=96, **options):
+    from metallix_b200.engine import Engine
+    folder, _, _, page = folders[name]
+    return Engine.from_folder(folder, dtype=dtype, page_tokens=page, num_pages=pages,
+                              max_requests=options.pop("max_requests", 8), **options)
+
+
+# ------------------------------------------------ configuration (no GPU needed)
+def test_configuration_round_trip_and_registry():
+    from metallix_b200.config import ConfigError, ZitezenConfig, parse_config, resolve
+    for raw in (SMALL, WIDE, BARE):
+        config = parse_config(raw)
+        assert isinstance(config, ZitezenConfig) and resolve(raw).kind == "zitezen"
+        assert ZitezenConfig.from_dict(config.to_dict()) == config
+        assert json.loads(json.dumps(config.to_dict())) == config.to_dict()
+        assert list(config.layer_order()) == plain.order_of_layers(raw)
+        shapes, s, w = config.tensor_shapes(), raw["streams"], raw["width"]
+        for index, spec in enumerate(raw["layers"]):
+            assert shapes[f"l{index}.hc1.mix"] == (s, s) and shapes[f"l{index}.norm1.alpha"] == ()
+            assert (f"l{index}.mlp.up" in shapes) == bool(spec["mlp"]) == (f"l{index}.hc2.in" in shapes)
+            mixer = spec["mixer"]
+            if spec["type"] == "mlstm":
+                assert shapes[f"l{index}.mix.v"] == (mixer["heads"] * mixer["vdim"], w)
+                assert shapes[f"l{index}.mix.f.b"] == (mixer["heads"],)
+            elif spec["type"] == "latent_attention":
+                assert shapes[f"l{index}.mix.dkv"] == (mixer["kv_rank"] + mixer["rot_dim"], w)
+                assert shapes[f"l{index}.mix.uq"] == (mixer["heads"] * (mixer["dim"] + mixer["rot_dim"]), mixer["q_rank"])
+            else:
+                assert shapes[f"l{index}.mix.left.g"] == (mixer["left"]["heads"], w)
+                assert shapes[f"l{index}.mix.left.v"] == (mixer["left"]["kv_heads"] * mixer["left"]["vdim"], w)
+                assert shapes[f"l{index}.mix.right.norm"] == (mixer["right"]["heads"] * mixer["right"]["vdim"],)
+        model = config.to_model_spec()
+        runs = plain.order_of_layers(raw)
+        assert [run.layer for run in model.order] == runs and model.streams == s
+        assert len({run.cache_entry() for run in model.order}) == len(runs)     # a pass keeps a cache of its own
+    refusals = [
+        ("UnsupportedLayerType", lambda c: c["layers"][0].update(type="attention")),
+        ("InvalidGroupedQueryLayout", lambda c: c["layers"][2]["mixer"]["left"].update(kv_heads=3)),
+        ("InvalidRotaryWidth", lambda c: c["layers"][2]["mixer"]["left"]["rot"].update(dims=18)),
+        ("InvalidRotaryWidth", lambda c: c["layers"][1]["mixer"]["rot"].update(dims=8)),
+        ("UnsupportedFeedForward", lambda c: c["layers"][1]["mlp"].update(kind="routed")),
+        ("MissingDimension", lambda c: c["layers"][0]["mixer"].update(vdim=0)),
+        ("Json", lambda c: c["layers"][0]["mixer"].update(gate_cap=0.0)),
+        ("Json", lambda c: c.update(loop={"start": 2, "stop": 5, "times": 2})),
+        ("Json", lambda c: c.update(streams=9)),
+        ("MissingDimension", lambda c: c.update(layers=[]))]
+    for kind, change in refusals:
+        raw = json.loads(json.dumps(SMALL))
+        change(raw)
+        with pytest.raises(ConfigError) as caught:
+            parse_config(raw)
+        assert caught.value.kind == kind
+    without = json.loads(json.dumps(SMALL))
+    del without["loop"]
+    assert list(parse_config(without).layer_order()) == [0, 1, 2, 3]
+
+
+def test_random_weights_by_kind_of_tensor(tmp_path):
+    from metallix_b200.config import ZitezenConfig
+    from metallix_b200.weights import CheckpointError, load_tensors, random_tensors, write_model_folder
+    config = ZitezenConfig.from_dict(SMALL)
+    tensors = random_tensors(config, 3, dtype="float32")
+    assert abs(float(tensors["l0.norm1"].mean()) - 1.0) < 0.05 and float(tensors["l0.norm1.b"].abs().max()) <= 0.1
+    assert tensors["final.norm.alpha"].shape == () and abs(float(tensors["final.norm.alpha"]) - 1.0) <= 0.1
+    mix = tensors["l1.hc2.mix"]
+    assert float((mix - torch.eye(3)).abs().max()) <= 0.1 and float(mix.diagonal().min()) >= 0.9
+    assert float(tensors["l2.mix.right.i"].abs().max()) < 0.2
+    folder = write_model_folder(str(tmp_path / "m"), config, 3)
+    loaded = load_tensors(folder, config)
+    assert set(loaded) == set(config.tensor_shapes()) and "l0.norm2" not in loaded
+    other = json.loads(json.dumps(SMALL))
+    other["layers"][2]["mixer"]["right"]["vdim"] = 41
+    with pytest.raises(CheckpointError):
+        load_tensors(folder, ZitezenConfig.from_dict(other))
+
+
+def test_cache_needs_of_a_looped_model_with_mixers_side_by_side():
+    """Every run gets an entry of its own; a mixer made of two has a need per
+    member; the pool's bytes per page count a one-plane latent once."""
+    from metallix_b200.cache import PagedCache
+    from metallix_b200.config import ZitezenConfig
+    from metallix_b200.config.spec import CacheNeed
+    spec = ZitezenConfig.from_dict(SMALL).to_model_spec()
+    assert spec.num_cache_entries() == 8
+    left = CacheNeed(kind="kv_pages", kv_heads=2, head_dim=24)
+    state = CacheNeed(kind="state", state_shape=(7,))
+    both = CacheNeed(kind="several", members=(left, state))
+    shared = CacheNeed(kind="kv_pages", kv_heads=1, head_dim=26, planes=1)
+    assert both.has_state() and not left.has_state() and both.flat() == (left, state)
+    assert shared.group_key() != CacheNeed(kind="kv_pages", kv_heads=1, head_dim=26).group_key()
+    cache = PagedCache([state, shared, both, shared, both], 4, 6, 3, torch.float32, "cpu", allocate=False)
+    assert len(cache.groups) == 2 and cache.groups[0].entries == [1, 3] and cache.groups[1].entries == [(2, 0), (4, 0)]
+    assert PagedCache.page_bytes([state, shared, both], 4, torch.float32) == 4 * 4 * (26 + 2 * 2 * 24)
+
+
+def test_the_plain_side_carries_its_state_and_ignores_what_follows():
+    """The plain implementation itself: a sequence's logits do not change when
+    more tokens follow; the recurrence run in two halves, its state handed on,
+    equals one run; a cap keeps the gates inside (-cap, cap)."""
+    from metallix_b200.config import ZitezenConfig
+    rng = np.random.default_rng(0)
+    shapes = ZitezenConfig.from_dict(BARE).tensor_shapes()
+    tensors = {name: rng.normal(size=shape) * (0.1 if len(shape) <= 1 else 0.3) for name, shape in shapes.items()}
+    ids = random_ids(1, 30, 97)
+    whole = plain.forward_logits(BARE, tensors, ids)
+    assert np.allclose(plain.forward_logits(BARE, tensors, ids[:19]), whole[:19], atol=1e-10)
+    q, k, v = rng.normal(size=(40, 5)), rng.normal(size=(40, 5)), rng.normal(size=(40, 7))
+    log_i, log_f = plain.capped_gates(rng.normal(size=40) * 30.0, rng.normal(size=40) * 30.0, 6.0)
+    assert np.abs(log_i).max() < 6.0 and log_f.max() < 0.0 and log_f.min() > -6.01
+    once, _ = plain.matrix_memory(q, k, v, log_i, log_f)
+    first, state = plain.matrix_memory(q[:17], k[:17], v[:17], log_i[:17], log_f[:17])
+    second, _ = plain.matrix_memory(q[17:], k[17:], v[17:], log_i[17:], log_f[17:], state)
+    assert np.allclose(np.concatenate([first, second]), once, atol=1e-12)
+
+
+# --------------------------------------------------------- mechanisms alone
+gpu = pytest.mark.gpu
+
+
+def dev(array, dtype=torch.float32):
+    return torch.tensor(np.asarray(array), dtype=dtype, device="cuda")
+
+
+def rounded(array, dtype):
+    return torch.tensor(np.asarray(array), dtype=dtype).double().numpy()
+
+
+@gpu
+@pytest.mark.parametrize("streams, width, rows", [(1, 72, 5), (2, 256, 9), (3, 331, 4), (8, 64, 3)])
+@pytest.mark.parametrize("result_dtype", [torch.float32, torch.bfloat16])
+def test_streams_write_read_and_tanh_norm(streams, width, rows, result_dtype):
+    """One kernel: a result joins all streams through the mixing matrix, the
+    next mixture is read and passes the tanh norm; also on chosen rows only,
+    without a result, and without a norm."""
+    from metallix_b200 import ops
+    rng = np.random.default_rng(streams * width)
+    x = rng.normal(size=(streams, rows, width)) * 2.0
+    y = rounded(rng.normal(size=(rows, width + 8)) * 3.0, result_dtype)[:, 3:3 + width]     # a column range of a wider product
+    mixing, out_w, in_w = rng.normal(size=(streams, streams)), rng.normal(size=streams), rng.normal(size=streams)
+    scale, gain, offset, alpha = rng.uniform(0.5, 1.5, width), rng.uniform(0.5, 1.5, width), rng.normal(size=width), 0.37
+    f32 = lambda a: dev(a).double().cpu().numpy()
+    new = plain.write_streams(f32(x), f32(mixing), f32(out_w), y * f32(scale))
+    want = plain.tanh_norm(plain.read_streams(new, f32(in_w)), f32(gain), f32(offset), float(np.float32(alpha)))
+    wide = dev(np.pad(y, ((0, 0), (3, 5))), result_dtype)
+    for out_dtype, tolerance in ((torch.float32, 2e-5), (torch.bfloat16, 2e-2)):
+        held = dev(x.transpose(1, 0, 2)).contiguous()
+        got = ops.stream_mix(held, result=wide[:, 3:3 + width], channel_scale=dev(scale), mix=dev(mixing),
+                             out_weights=dev(out_w), in_weights=dev(in_w), alpha=dev([alpha]), norm_weight=dev(gain),
+                             norm_bias=dev(offset), out_dtype=out_dtype)
+        assert np.abs(held.double().cpu().numpy().transpose(1, 0, 2) - new).max() < 2e-5
+        assert np.abs(got.double().cpu().numpy() - want).max() < tolerance
+    # chosen rows, the plain sum, nothing stored
+    held = dev(x.transpose(1, 0, 2)).contiguous()
+    before = held.clone()
+    picked = [rows - 1, 0]
+    got = ops.stream_mix(held, result=wide[:, 3:3 + width], channel_scale=dev(scale), mix=dev(mixing), out_weights=dev(out_w),
+                         out_dtype=torch.float32, rows_index=dev(picked, torch.int32), keep_streams=False)
+    assert torch.equal(held, before)
+    assert np.abs(got.double().cpu().numpy() - new.sum(axis=0)[picked]).max() < 5e-5
+    # no result: a read alone
+    got = ops.stream_mix(held, in_weights=dev(in_w), out_dtype=torch.float32)
+    assert np.abs(got.double().cpu().numpy() - plain.read_streams(f32(x), f32(in_w))).max() < 2e-5
+    # the write alone
+    ops.stream_mix(held, result=wide[:, 3:3 + width], channel_scale=dev(scale), mix=dev(mixing), out_weights=dev(out_w), read=False)
+    assert np.abs(held.double().cpu().numpy().transpose(1, 0, 2) - new).max() < 2e-5
+
+
+@gpu
+def test_tanh_norm_as_a_norm_part_and_small_sums():
+    from metallix_b200 import ops
+    from metallix_b200.config.spec import PartSpec
+    from metallix_b200.parts.registry import Runtime, WeightStore, build_part
+    rng = np.random.default_rng(5)
+    gain, offset, alpha = rng.uniform(0.5, 1.5, 40), rng.normal(size=40), 0.8
+    runtime = Runtime(device=torch.device("cuda"), dtype=torch.float32, max_positions=16)
+    store = WeightStore({"n": dev(gain), "n.b": dev(offset), "n.alpha": dev(alpha)})
+    norm = build_part("norm", PartSpec("dynamic_tanh", {"size": 40, "weight": "n", "bias": "n.b", "alpha": "n.alpha"}),
+                      store, runtime)
+    x, d = rng.normal(size=(6, 40)), rng.normal(size=(6, 40))
+    f32 = lambda a: dev(a).double().cpu().numpy()
+    want = lambda v: plain.tanh_norm(v, f32(gain), f32(offset), float(np.float32(alpha)))
+    assert np.abs(norm.forward(dev(x), torch.float32).double().cpu().numpy() - want(f32(x))).max() < 1e-5
+    rows = dev([4, 1], torch.int32)
+    assert np.abs(norm.forward(dev(x), torch.float32, rows_index=rows).double().cpu().numpy() - want(f32(x))[[4, 1]]).max() < 1e-5
+    residual = dev(x)
+    got = norm.add_forward(residual, dev(d), torch.float32)
+    assert np.abs(residual.double().cpu().numpy() - (f32(x) + f32(d))).max() < 1e-6
+    assert np.abs(got.double().cpu().numpy() - want(f32(x) + f32(d))).max() < 1e-5
+    a, b = dev(x, torch.bfloat16), dev(d, torch.bfloat16)
+    total = ops.weighted_sum(a, b, 0.6, -1.1)
+    assert np.abs(total.double().cpu().numpy() - (0.6 * a.double().cpu().numpy() - 1.1 * b.double().cpu().numpy())).max() < 1e-5
+    squared = ops.relu_squared(dev(x))
+    assert np.abs(squared.double().cpu().numpy() - np.square(np.maximum(f32(x), 0.0))).max() < 1e-6
+
+
+@gpu
+@pytest.mark.parametrize("heads, dim, vdim", [(3, 8, 20), (1, 16, 33), (2, 64, 64), (4, 5, 4), (2, 130, 96)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_matrix_memory_kernel(heads, dim, vdim, dtype):
+    """The recurrence over three requests of unequal length in one launch (one
+    of them a single token, one a padding row), then continued in a second
+    launch from the state the first left, against the plain recurrence run in
+    one piece; a slot is zeroed and used again."""
+    from metallix_b200 import ops
+    rng = np.random.default_rng(heads * dim + vdim)
+    cap, lengths = 7.0, [19, 1, 0, 11]
+    k_size, v_size = heads * dim, heads * vdim
+    columns = 2 * k_size + 2 * v_size + 2 * heads + 5
+    at = {"q": 2, "k": 2 + k_size, "v": 2 + 2 * k_size, "g": 2 + 2 * k_size + v_size, "i": 2 + 2 * k_size + 2 * v_size}
+    at["f"] = at["i"] + heads
+    total = 2 * sum(lengths)
+    proj = rng.normal(size=(total, columns))
+    proj[:, at["i"]:at["f"] + heads] *= 6.0       # gates that reach the cap and that do not
+    proj = rounded(proj, dtype)
+    i_bias, f_bias = rng.normal(size=heads), rng.normal(size=heads) + 2.0
+    f32 = lambda a: dev(a).double().cpu().numpy()
+    slots = [2, 0, 1, 3]
+    state = torch.full((5, ops.mlstm_state_values(heads, dim, vdim)), 3.0, device="cuda")
+    for slot in slots:
+        state[slot].zero_()
+    device_proj = dev(proj, dtype)
+    outs = {}
+    cursor = 0
+    for half in range(2):
+        starts = []
+        for length in lengths:
+            starts.append(cursor)
+            cursor += length
+        got = ops.mlstm_scan(device_proj, (at["q"], at["k"], at["v"], at["i"], at["f"]), dev(i_bias), dev(f_bias), cap,
+                             state, dev(starts, torch.int32), dev(lengths, torch.int32), dev(slots, torch.int32),
+                             heads, dim, vdim)
+        ops.check_status("cuda")
+        for row, (start, length) in enumerate(zip(starts, lengths)):
+            outs.setdefault(row, []).append(got[start:start + length].double().cpu().numpy())
+    assert float(state[4].min()) == 3.0 and float(state[1].abs().max()) == 0.0     # untouched slot, padding row's slot
+    tolerance = 2e-4
+    for row, length in enumerate(lengths):
+        if not length:
+            continue
+        rows = np.concatenate([np.arange(s, s + length) for s in
+                               (sum(lengths[:row]), sum(lengths) + sum(lengths[:row]))])
+        x = proj[rows]
+        for h in range(heads):
+            log_i, log_f = plain.capped_gates(x[:, at["i"] + h] + f32(i_bias)[h], x[:, at["f"] + h] + f32(f_bias)[h], cap)
+            want, _ = plain.matrix_memory(x[:, at["q"] + h * dim:at["q"] + (h + 1) * dim] * dim ** -0.5,
+                                          x[:, at["k"] + h * dim:at["k"] + (h + 1) * dim],
+                                          x[:, at["v"] + h * vdim:at["v"] + (h + 1) * vdim], log_i, log_f)
+            have = np.concatenate(outs[row])[:, h * vdim:(h + 1) * vdim]
+            assert np.abs(have - want).max() < tolerance * max(1.0, np.abs(want).max()), (row, h)
+    # the per-head norm and the output gate that follow
+    memory_out = dev(rng.normal(size=(7, v_size)))
+    weight, gate = rng.uniform(0.5, 1.5, v_size), rounded(rng.normal(size=(7, v_size)), dtype)
+    got = ops.head_norm_gate(memory_out, dev(weight), dev(gate, dtype), heads, 1e-5, dtype)
+    want = plain.unit_rms(memory_out.double().cpu().numpy().reshape(7, heads, vdim), 1e-5).reshape(7, v_size) \
+        * f32(weight) * plain.sigmoid(gate)
+    assert np.abs(got.double().cpu().numpy() - want).max() < (1e-5 if dtype == torch.float32 else 3e-2)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rank, rot, heads, dim", [(20, 6, 4, 12), (48, 16, 2, 32), (12, 4, 3, 8), (96, 2, 1, 5)])
+def test_latent_rows_into_the_cache_and_rotated_query_parts(dtype, rank, rot, heads, dim):
+    from metallix_b200 import ops
+    rng = np.random.default_rng(rank + rot)
+    tokens, page, pages, eps, base = 23, 4, 8, 1e-5, 100.0
+    positions = rng.permutation(40)[:tokens]
+    slots = rng.permutation(page * pages)[:tokens]
+    slots[3] = -1
+    x = rounded(rng.normal(size=(tokens, rank + rot + 3)), dtype)
+    gain = rng.uniform(0.5, 1.5, rank)
+    frequency = base ** (-2.0 * np.arange(rot // 2) / rot)
+    angle = torch.arange(48, dtype=torch.float64)[:, None] * torch.tensor(frequency)[None, :]
+    cos, sin = torch.cos(angle).float().cuda().contiguous(), torch.sin(angle).float().cuda().contiguous()
+    cache = torch.full((pages, 1, 1, page, rank + rot), 7.0, dtype=dtype, device="cuda")
+    ops.latent_cache(dev(x, dtype)[:, :rank + rot], dev(gain), eps, rank, cache, dev(slots, torch.int32),
+                     dev(positions, torch.int32), cos, sin, True)
+    ops.check_status("cuda")
+    f32 = lambda a: dev(a).double().cpu().numpy()
+    want_latent = plain.unit_rms(x[:, :rank], eps) * f32(gain)
+    want_key = plain.turn(x[:, rank:rank + rot].reshape(tokens, 1, rot), positions, base, rot, neighbours=True)[:, 0]
+    got = cache.double().cpu().numpy().reshape(pages * page, rank + rot)
+    tolerance = 1e-5 if dtype == torch.float32 else 3e-2
+    written = np.zeros(pages * page, dtype=bool)
+    for t, slot in enumerate(slots):
+        if slot < 0:
+            continue
+        written[slot] = True
+        assert np.abs(got[slot, :rank] - want_latent[t]).max() < tolerance
+        assert np.abs(got[slot, rank:] - want_key[t]).max() < tolerance
+    assert (got[~written] == 7.0).all()
+    q = rounded(rng.normal(size=(tokens, heads * (dim + rot))), dtype)
+    target = torch.zeros((tokens, heads, rank + rot), dtype=dtype, device="cuda")
+    ops.rotate_into(dev(q, dtype), dim, dim + rot, target, rank, rot, dev(positions, torch.int32), cos, sin, True)
+    want = plain.turn(q.reshape(tokens, heads, dim + rot)[:, :, dim:], positions, base, rot, neighbours=True)
+    got = target.double().cpu().numpy()
+    assert np.abs(got[:, :, rank:] - want).max() < tolerance and (got[:, :, :rank] == 0.0).all()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("planes, heads, kv_heads, dim, vdim, cap, per_head", [
+    (2, 4, 2, 24, 24, 5.0, True), (2, 4, 2, 24, 16, 0.0, True), (1, 5, 1, 26, 20, 0.0, False),
+    (1, 2, 1, 300, 280, 0.0, False), (2, 6, 6, 64, 64, 30.0, True), (2, 3, 1, 8, 8, 2.0, False)])
+def test_general_attention_kernel_one_key_that_stands_out(dtype, planes, heads, kv_heads, dim, vdim, cap, per_head):
+    """The general kernel with a cap on the scores, a gate per head, values
+    narrower than the rows and rows that are keys and values at once. One far
+    key among hundreds is made to stand out for the last query, and the keys
+    at a page's border for others, so that a key that is lost or misplaced
+    shows."""
+    from metallix_b200 import ops
+    rng = np.random.default_rng(dim * heads + vdim)
+    page, context, tail = 8, 333, 21            # the last `tail` positions are this step's queries
+    pages = -(-context // page)
+    order = rng.permutation(pages + 3)[:pages]  # pages scattered over the pool
+    rows = rng.normal(size=(context, kv_heads, dim)) * 0.5
+    values = rows[:, :, :vdim] if planes == 1 else rng.normal(size=(context, kv_heads, dim))
+    q = rng.normal(size=(tail, heads, dim)) * 0.5
+    far = 5
+    rows[far] *= 6.0
+    q[-1] = np.repeat(rows[far], heads // kv_heads, axis=0) * 1.5        # the last query looks for position 5
+    for offset, key in ((3, page * 17 - 1), (4, page * 17), (5, context - tail + 2)):   # a page's last and first row
+        rows[key] *= 5.0
+        q[offset] = np.repeat(rows[key], heads // kv_heads, axis=0) * 1.2
+    rows, q, values = rounded(rows, dtype), rounded(q, dtype), rounded(values, dtype)
+    if planes == 1:
+        values = rows[:, :, :vdim]
+    pool = torch.zeros((pages + 3, planes, kv_heads, page, dim), dtype=dtype, device="cuda")
+    for p in range(pages):
+        chunk = slice(p * page, min((p + 1) * page, context))
+        n = chunk.stop - chunk.start
+        pool[order[p], 0, :, :n] = dev(rows[chunk].transpose(1, 0, 2), dtype)
+        if planes == 2:
+            pool[order[p], 1, :, :n, :values.shape[2]] = dev(values[chunk].transpose(1, 0, 2), dtype)
+    gate = rounded(rng.normal(size=(tail, heads if per_head else heads * vdim)), dtype)
+    out = torch.empty((tail, heads, vdim), dtype=dtype, device="cuda")
+    positions = np.arange(context - tail, context)
+    starts = [0, 16] if tail > 16 else [0]
+    ops.paged_attention_tile(dev(q, dtype), pool, out, dev(order[None, :], torch.int32), dev([0] * len(starts), torch.int32),
+                             dev(starts, torch.int32), dev([min(16, tail - s) for s in starts], torch.int32),
+                             dev(positions, torch.int32), 0.3, gate=dev(gate, dtype), softcap=cap, gate_per_head=per_head)
+    ops.check_status("cuda")
+    group = heads // kv_heads
+    k_all, v_all = np.repeat(rows, group, axis=1), np.repeat(values[:, :, :vdim], group, axis=1)
+    want = np.zeros((tail, heads, vdim))
+    weight_on_far = 0.0
+    for t, p in enumerate(positions):
+        s = np.einsum("hd,jhd->hj", q[t], k_all[:p + 1]) * 0.3
+        if cap:
+            s = cap * np.tanh(s / cap)
+        w = np.exp(s - s.max(axis=1, keepdims=True))
+        w /= w.sum(axis=1, keepdims=True)
+        want[t] = np.einsum("hj,jhv->hv", w, v_all[:p + 1])
+        if t == tail - 1:
+            weight_on_far = w[:, far].min()
+    want *= plain.sigmoid(gate)[:, :, None] if per_head else plain.sigmoid(gate).reshape(tail, heads, vdim)
+    assert weight_on_far > 5.0 / context      # the far key weighs many times its share in the last output, capped or not
+    assert np.abs(out.double().cpu().numpy() - want).max() < (2e-5 if dtype == torch.float32 else 3e-2)
+
+
+# ------------------------------------------------- the engine: whole prompts
+def reference_logits(folders, name, requests):
+    _, config, tensors, _ = folders[name]
+    return {key: plain.forward_logits(config, tensors, ids) for key, ids in requests.items()}
+
+
+def some_requests(name, seed, lengths):
+    vocab = MODELS[name][0]["vocab"]
+    return {f"r{n}": random_ids(seed + n, length, vocab) for n, length in enumerate(lengths)}
+
+
+@gpu
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_whole_prompts_layer_by_layer(folders, name, dtype):
+    """A prompt in one step: the sum of the streams after every layer run,
+    then the logits at every position; a single token; two tokens."""
+    from metallix_b200.engine import StepEntry
+    engine = make_engine(folders, name, dtype)
+    _, config, tensors, _ = folders[name]
+    ids = random_ids(7, 45, config["vocab"])
+    want_taps = []
+    want = plain.forward_logits(config, tensors, ids, want_taps)
+    got_taps = []
+    logits = engine.step([StepEntry("a", ids, list(range(len(ids))))], tap=lambda i, r: got_taps.append(r.double().cpu().numpy()))
+    engine.check()
+    assert len(got_taps) == len(want_taps) == len(plain.order_of_layers(config))
+    slack = 1.0 if dtype == "float32" else 4.0
+    for index, (have, should) in enumerate(zip(got_taps, want_taps)):
+        assert np.abs(have - should).max() < slack * bound(name, dtype) * max(1.0, np.abs(should).max()), index
+    assert np.abs(logits.double().cpu().numpy() - want).max() < bound(name, dtype)
+    engine.release("a")
+    for length in (1, 2):
+        logits = engine.step([StepEntry("b", ids[:length], list(range(length)))])
+        assert np.abs(logits.double().cpu().numpy() - want[:length]).max() < bound(name, dtype)
+        engine.release("b")
+    engine.check()
+
+
+@gpu
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_decoding_and_portions_against_whole_prompts(folders, name, dtype):
+    """The same requests as whole prompts, with their tails decoded one by
+    one, and in portions of changing size down to two tokens (and one): the
+    cache, the state and the rows' bookkeeping give the plain logits each time."""
+    from metallix_b200.engine import StepEntry
+    requests = some_requests(name, 40, (75, 9, 33))
+    reference = reference_logits(folders, name, requests)
+    for schedule in (cuts.whole(requests), cuts.tail_by_one(requests, tail=20), cuts.ragged(requests)):
+        engine = make_engine(folders, name, dtype, pages=48, max_requests=2)
+        _, seen = cuts.replay(engine, schedule, reference, StepEntry)
+        judge(name, dtype, seen, reference)
+
+
+@gpu
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_mixed_batches_with_pages_and_slots_that_come_back(folders, name, dtype):
+    """Up to four requests live at once in a pool made for just that many:
+    portions beside single tokens, requests that sit a step out, ended
+    requests whose pages and state slots the next ones take over. Each
+    position's logits equal those of the request run alone."""
+    from metallix_b200.engine import StepEntry
+    requests = some_requests(name, 60, (70, 41, 5, 90, 23, 1, 37, 64))
+    reference = reference_logits(folders, name, requests)
+    steps, peak = cuts.mixed(requests, seed=5, max_live=4)
+    page = folders[name][3]
+    engine = make_engine(folders, name, dtype, pages=-(-peak // page), max_requests=4)
+    _, mixed_seen = cuts.replay(engine, steps, reference, StepEntry)
+    judge(name, dtype, mixed_seen, reference)
+    assert engine.manager.pages_reused() > 0 and len(requests) > engine.manager.max_requests()
+    if dtype == "float32":     # against the engine itself, each request alone: rounding of the products only
+        alone = make_engine(folders, name, dtype, pages=48, max_requests=2)
+        _, alone_seen = cuts.replay(alone, cuts.whole(requests), reference, StepEntry)
+        gap = max(float(np.abs(row - alone_seen[key]).max()) for key, row in mixed_seen.items())
+        assert gap < 0.3 * bound(name, dtype)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_captured_steps(folders, dtype):
+    """Three requests decoded together for 150 steps (captured graphs), one of
+    them leaving on the way and another joining: state and pages stay theirs."""
+    from metallix_b200.engine import StepEntry
+    name = "small"
+    requests = some_requests(name, 80, (190, 170, 120))
+    reference = reference_logits(folders, name, requests)
+    engine = make_engine(folders, name, dtype, pages=80, max_requests=3)
+    heads = {"r0": 30, "r1": 12}
+    worst = 0.0
+    logits = engine.step([StepEntry(k, requests[k][:n], [n - 1]) for k, n in heads.items()])
+    at = dict(heads)
+    for step in range(160):
+        if step == 40:       # r2 joins with a prompt of its own beside the decoded tokens
+            at["r2"] = 0
+        entries, rows = [], []
+        for key in list(at):
+            ids = requests[key]
+            if at[key] >= len(ids):
+                engine.release(key)
+                del at[key]
+                continue
+            count = 17 if key == "r2" and at[key] == 0 else 1
+            entries.append(StepEntry(key, ids[at[key]:at[key] + count], [count - 1]))
+            rows.append(reference[key][at[key] + count - 1])
+            at[key] += count
+        if not entries:
+            break
+        logits = engine.step(entries)
+        worst = max(worst, float(np.abs(logits.double().cpu().numpy() - np.stack(rows)).max()))
+    engine.check()
+    assert worst < bound(name, dtype)
+    if engine.graphs is not None:
+        assert engine.graphs.sizes_captured()      # decode steps did run as graphs
+
+
+@gpu
+def test_fork_copies_pages_and_state(folders):
+    from metallix_b200.engine import StepEntry
+    name = "bare"
+    _, config, tensors, _ = folders[name]
+    ids = random_ids(3, 40, config["vocab"])
+    other = ids[:22] + random_ids(4, 18, config["vocab"])
+    engine = make_engine(folders, name, "float32", pages=64)
+    engine.step([StepEntry("p", ids[:22], [])])
+    engine.fork("p", "c")
+    a = engine.step([StepEntry("p", ids[22:], list(range(18))), StepEntry("c", other[22:], list(range(18)))])
+    engine.check()
+    want = np.concatenate([plain.forward_logits(config, tensors, ids)[22:], plain.forward_logits(config, tensors, other)[22:]])
+    assert np.abs(a.double().cpu().numpy() - want).max() < TOL["float32"]
+
+
+# ------------------------------------- generation, scheduler, command line
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(folders, dtype):
+    """``generate`` (scheduler, continuous batching, captured decode steps):
+    every generated token is the plain side's argmax, or (bfloat16) within a
+    near tie of it."""
+    from metallix_b200.engine.generate import generate
+    name = "small"
+    _, config, tensors, _ = folders[name]
+    engine = make_engine(folders, name, dtype, pages=64, max_requests=4)
+    prompts = [random_ids(90 + n, length, config["vocab"]) for n, length in enumerate((5, 31, 1, 12, 18, 2))]
+    results = generate(engine, prompts, max_new_tokens=12, eos_ids=())
+    for prompt, result in zip(prompts, results):
+        assert len(result.generated_ids) == 12 and not result.failed
+        ids = list(prompt)
+        for token in result.generated_ids:
+            row = plain.forward_logits(config, tensors, ids)[-1]
+            best = int(np.argmax(row))
+            if token != best:
+                assert dtype == "bfloat16" and row[best] - row[token] < 0.3, (dtype, token, best)
+            ids.append(token)
+
+
+@gpu
+def test_trace_program_and_command_line(folders, tmp_path):
+    """bin/trace_run on a mixed schedule and bin/mxb gen, as programs."""
+    name = "bare"
+    folder, config, tensors, page = folders[name]
+    requests = some_requests(name, 70, (30, 12, 44))
+    reference = reference_logits(folders, name, requests)
+    steps, peak = cuts.mixed(requests, seed=9, max_live=2, decode_tail=6)
+    out = tmp_path / "logits"
+    done = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                           "--out", str(out), "--max-tokens", str(peak)],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [line for line in done.stdout.splitlines() if line.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    offsets = {}
+    for step in steps:
+        for e in step["entries"]:
+            offsets.setdefault(e["id"], 0)
+        want = cuts.expected_rows(step, offsets, reference)
+        if want is not None:
+            got = np.fromfile(out / f"{step['step']}.f32", dtype="<f4").reshape(want.shape)
+            assert np.abs(got - want).max() < TOL["float32"]
+        for e in step["entries"]:
+            offsets[e["id"]] += len(e["tokens"])
+    prompt = requests["r1"]
+    done = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mxb"), "gen", "--model", folder, "--input-ids",
+                           ",".join(map(str, prompt)), "--max-tokens", "4", "--dtype", "float32", "--verify-cache"],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    receipt = json.loads(done.stdout.strip().splitlines()[-1])
+    ids = list(prompt)
+    for _ in range(4):
+        ids.append(int(np.argmax(plain.forward_logits(config, tensors, ids)[-1])))
+    assert receipt["generated_ids"] == ids[len(prompt):]
+    assert receipt["operation"] == "zitezen_greedy_cached_generation"
+    assert receipt["cache_comparisons"]["logits_within_bound"]
