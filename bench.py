@@ -6,6 +6,7 @@
     python bench.py --shape 32b                                   prefill and decode at 8,192-token contexts
     python bench.py --workload decode|prefill|gemm|attention|pick ...   small fixed workloads for profilers
     python bench.py --design mekazen                              the Mekazen decoder beside Qwen3 at equal layer sizes
+    python bench.py --design zitezen                              the Zitezen decoder beside Qwen3 at equal width, heads and feed-forward
 
 Default workload: a Qwen3-0.6B-shaped model (28 layers,
 hidden 1024, 16 query and 8 key/value heads of 128, SwiGLU 3072, vocabulary
@@ -660,8 +661,12 @@ def workload(args):
 
     if args.design:   # the same workloads on the other design, at this shape's layer sizes
         hidden, heads, kv_heads, dim, inter = DESIGN_SIZES[{"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape]]
-        other = _mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or 4096)
-        config = parse_config(dict(other, layers=other["layers"][:1] * layers))
+        if args.design == "zitezen":   # its layers come in fours: the first `layers` of them
+            other = _zitezen(hidden, heads, kv_heads, dim, inter, {"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape])
+            config = parse_config(dict(other, layers=(other["layers"] * layers)[:layers]))
+        else:
+            other = _mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or 4096)
+            config = parse_config(dict(other, layers=other["layers"][:1] * layers))
     else:
         config = parse_config(dict(raw, num_hidden_layers=layers))
     pages = args.batch * (-(-(args.prompt_len + 64) // args.page_tokens) + 1) + 64 * 16 // args.page_tokens
@@ -736,6 +741,62 @@ def _mekazen(hidden, heads, kv_heads, dim, inter, chunk):
             "logit_softcap": 30.0, "layers": [layer] * DESIGN_LAYERS}
 
 
+def _engine_numbers(config, args, peak, rng, warmup, steps):
+    """One model through the engine: a prompt of ``args.prompt_len`` tokens in
+    one step (median of 5), then decode steps of 1 and 8 requests behind such
+    prompts (median of 3 runs of ``steps``), with the bytes a decode step must
+    read (weights, cached rows, recurrent state) against the copy bandwidth."""
+    import statistics as stats
+    import numpy as np
+    import torch
+    from metallix_b200 import ops
+    from metallix_b200.engine import Engine, StepEntry
+    span = args.prompt_len + warmup + steps + 64
+    engine = Engine.from_random(config, seed=0, dtype="bfloat16", page_tokens=16,
+                                num_pages=8 * (-(-span // 16)) + 64, max_requests=10,
+                                max_context=args.context, gemm_backend=args.gemm)
+    device = engine.device
+
+    def one_prefill(tokens):
+        engine.step([StepEntry("prefill", tokens, [len(tokens) - 1])])
+        engine.release("prefill")
+
+    prompt = rng.integers(0, DESIGN_VOCAB, size=args.prompt_len).tolist()
+    for _ in range(4):   # launched kernel by kernel, seen, captured, replayed
+        one_prefill(prompt)
+    prefill_ms = stats.median(timed(torch, device, lambda _: one_prefill(prompt), 1) for _ in range(5))
+    result = {"prefill_ms": prefill_ms, "prefill_tok_s": args.prompt_len / prefill_ms * 1e3}
+    state_bytes = sum(4 * int(np.prod(need.state_shape)) for whole in engine.cache.needs if whole is not None
+                      for need in whole.flat() if need.kind == "state")
+    for batch in (1, 8):
+        engine.release_all()
+        names = [f"r{i}" for i in range(batch)]
+        for first in range(0, batch, 4):
+            engine.step([StepEntry(n, rng.integers(0, DESIGN_VOCAB, size=args.prompt_len).tolist(), [])
+                         for n in names[first:first + 4]])
+        feed = rng.integers(0, DESIGN_VOCAB, size=(warmup + 3 * steps, batch))
+
+        def one(index):
+            engine.step([StepEntry(n, [int(feed[index, i])], [0]) for i, n in enumerate(names)])
+
+        for index in range(warmup):
+            one(index)
+        before = ops.launch_count()
+        runs = sorted(timed(torch, device, lambda index: one(warmup + r * steps + index), steps)
+                      for r in range(3))
+        launches = (ops.launch_count() - before) // 3
+        ms = runs[1] / steps
+        step_bytes = engine.model.weight_bytes() + batch * ((args.prompt_len + warmup + 1.5 * steps)
+                                                            * engine.cache.bytes_per_token() + 2 * state_bytes)
+        result[f"decode_b{batch}"] = {
+            "ms_per_step": ms, "tok_s": batch / ms * 1e3, "kernels_per_step": launches // steps,
+            "frac_of_copy_bandwidth": step_bytes / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
+    engine.check()
+    del engine
+    torch.cuda.empty_cache()
+    return result
+
+
 def design(args):
     """Prompt and decode throughput of the Mekazen decoder beside the Qwen3
     decoder with the same layer sizes (random weights, bfloat16), and each
@@ -758,50 +819,7 @@ def design(args):
             "mekazen": parse_config(_mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or args.context)),
             "qwen3": parse_config(dict(_qwen3(DESIGN_LAYERS, hidden, heads, kv_heads, inter, False),
                                        vocab_size=DESIGN_VOCAB, head_dim=dim))}
-        row = {}
-        for family, config in configs.items():
-            span = args.prompt_len + warmup + steps + 64
-            engine = Engine.from_random(config, seed=0, dtype="bfloat16", page_tokens=16,
-                                        num_pages=8 * (-(-span // 16)) + 64, max_requests=10,
-                                        max_context=args.context, gemm_backend=args.gemm)
-            device = engine.device
-
-            def one_prefill(tokens):
-                engine.step([StepEntry("prefill", tokens, [len(tokens) - 1])])
-                engine.release("prefill")
-
-            prompt = rng.integers(0, DESIGN_VOCAB, size=args.prompt_len).tolist()
-            for _ in range(4):   # launched kernel by kernel, seen, captured, replayed
-                one_prefill(prompt)
-            prefill_ms = statistics.median(timed(torch, device, lambda _: one_prefill(prompt), 1) for _ in range(5))
-            result = {"prefill_ms": prefill_ms, "prefill_tok_s": args.prompt_len / prefill_ms * 1e3}
-            for batch in (1, 8):
-                engine.release_all()
-                names = [f"r{i}" for i in range(batch)]
-                for first in range(0, batch, 4):
-                    engine.step([StepEntry(n, rng.integers(0, DESIGN_VOCAB, size=args.prompt_len).tolist(), [])
-                                 for n in names[first:first + 4]])
-                feed = rng.integers(0, DESIGN_VOCAB, size=(warmup + 3 * steps, batch))
-
-                def one(index):
-                    engine.step([StepEntry(n, [int(feed[index, i])], [0]) for i, n in enumerate(names)])
-
-                for index in range(warmup):
-                    one(index)
-                before = ops.launch_count()
-                runs = sorted(timed(torch, device, lambda index: one(warmup + r * steps + index), steps)
-                              for r in range(3))
-                launches = (ops.launch_count() - before) // 3
-                ms = runs[1] / steps
-                step_bytes = engine.model.weight_bytes() + batch * (args.prompt_len + warmup + 1.5 * steps) \
-                    * engine.cache.bytes_per_token()
-                result[f"decode_b{batch}"] = {
-                    "ms_per_step": ms, "tok_s": batch / ms * 1e3, "kernels_per_step": launches // steps,
-                    "frac_of_copy_bandwidth": step_bytes / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
-            engine.check()
-            row[family] = result
-            del engine
-            torch.cuda.empty_cache()
+        row = {family: _engine_numbers(config, args, peak, rng, warmup, steps) for family, config in configs.items()}
         out["sizes"][size] = row
 
     # ---- the kernels the design adds, beside their like, on one layer's rows
@@ -865,6 +883,183 @@ def design(args):
     return 0
 
 
+# Zitezen layers at the two sizes: per size the recurrence's (heads, key width, value width), the latent
+# attention's (heads, unrotated, rotated, value width, latent, query latent) and the recurrence beside the
+# grouped attention (which has the size's own heads). Eight layers: recurrence, latent attention with a
+# feed-forward, both side by side with a feed-forward, recurrence; twice. Two residual streams.
+ZITEZEN_SIZES = {"0.6b-layers": ((8, 64, 128), (16, 64, 32, 64, 256, 384), (4, 64, 128)),
+                 "8b-layers": ((8, 128, 512), (32, 128, 64, 128, 512, 1536), (8, 64, 256))}
+
+
+def _zitezen(hidden, heads, kv_heads, dim, inter, size):
+    memory, latent, beside = ZITEZEN_SIZES[size]
+    recurrence = lambda m: {"heads": m[0], "dim": m[1], "vdim": m[2], "gate_cap": 15.0}
+    rot = lambda dims: {"base": 1.0e4, "dims": dims}
+    through_latent = {"heads": latent[0], "dim": latent[1], "rot_dim": latent[2], "vdim": latent[3],
+                      "kv_rank": latent[4], "q_rank": latent[5], "scale": (latent[1] + latent[2]) ** -0.5,
+                      "rot": rot(latent[2])}
+    grouped = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+               "rot": rot(dim // 2)}
+    mlp = {"kind": "dense", "ff": inter}
+    four = [{"type": "mlstm", "mixer": recurrence(memory), "mlp": None},
+            {"type": "latent_attention", "mixer": through_latent, "mlp": mlp},
+            {"type": "parallel", "mixer": {"left": grouped, "right": recurrence(beside), "left_scale": 0.6,
+                                           "right_scale": 0.9}, "mlp": mlp},
+            {"type": "mlstm", "mixer": recurrence(memory), "mlp": None}]
+    return {"architecture": "Zitezen", "vocab": DESIGN_VOCAB, "width": hidden, "streams": 2, "norm": {"eps": 1e-5},
+            "layers": four * (DESIGN_LAYERS // 4)}
+
+
+def design_zitezen(args):
+    """Prompt and decode throughput of the Zitezen decoder beside the Qwen3
+    decoder with the same width, heads and feed-forward (random weights,
+    bfloat16, 8 layers), then each kernel the design adds beside the like
+    kernel of Qwen3: bytes that must move over time against the measured copy
+    bandwidth, or (the recurrence and the attention over a prompt) arithmetic
+    over time. One JSON line."""
+    import numpy as np
+    import torch
+    from metallix_b200 import ops, parse_config
+
+    peak, peak_source = peaks()
+    warmup, steps = max(args.warmup, 3), min(max(args.steps, 1), 64)
+    rng = np.random.default_rng(0)
+    out = {"design": "zitezen", "beside": "qwen3", "dtype": "bf16", "layers": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
+           "prompt_len": args.prompt_len, "peaks": peak_source, "sizes": {}}
+    for size, (hidden, heads, kv_heads, dim, inter) in ({} if args.kernels_only else DESIGN_SIZES).items():
+        configs = {"zitezen": parse_config(_zitezen(hidden, heads, kv_heads, dim, inter, size)),
+                   "qwen3": parse_config(dict(_qwen3(DESIGN_LAYERS, hidden, heads, kv_heads, inter, False),
+                                              vocab_size=DESIGN_VOCAB, head_dim=dim))}
+        out["sizes"][size] = {family: _engine_numbers(config, args, peak, rng, warmup, steps)
+                              for family, config in configs.items()}
+
+    def measure(function):
+        for _ in range(3):
+            function()
+        flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+        times = []
+        for _ in range(7):
+            flush.zero_()    # a buffer larger than L2 between the timed launches
+            times.append(timed(torch, "cuda", lambda _: function(), 1))
+        return statistics.median(times)
+
+    def gbs(bytes_moved, function):
+        ms = measure(function)
+        return {"us": ms * 1e3, "gb_s": bytes_moved / (ms * 1e-3) / 1e9,
+                "frac_of_copy_bandwidth": bytes_moved / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
+
+    def tflops(flops, function):
+        ms = measure(function)
+        return {"us": ms * 1e3, "tflop_s": flops / (ms * 1e-3) / 1e12,
+                "frac_of_bf16_matrix_peak": flops / (ms * 1e-3) / 1e12 / peak["bf16_tflops"]}
+
+    ops.require_cuda()
+    kernels = {}
+    size = "8b-layers" if not args.kernels_only else "0.6b-layers"
+    hidden, heads, kv_heads, dim, inter = DESIGN_SIZES[size]
+    memory, latent, _ = ZITEZEN_SIZES[size]
+    bf16, f32 = torch.bfloat16, torch.float32
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    prompt = args.prompt_len
+    for tokens in (8, prompt * 4):
+        # residual sum(s) and the next norm
+        streams = torch.randn(tokens, 2, hidden, device="cuda")
+        x = torch.randn(tokens, hidden, device="cuda")
+        delta = torch.randn(tokens, hidden, device="cuda").to(bf16)
+        ones = torch.ones(hidden, device="cuda")
+        mixing, pair, alpha = torch.eye(2, device="cuda"), torch.ones(2, device="cuda"), torch.ones(1, device="cuda")
+        kernels[f"sum_and_norm_{tokens}"] = {
+            "zitezen: two streams written and read, tanh norm": gbs(
+                tokens * hidden * (2 * 4 * 2 + 2 + 2), lambda: ops.stream_mix(
+                    streams, result=delta, channel_scale=ones, mix=mixing, out_weights=pair, in_weights=pair,
+                    alpha=alpha, norm_weight=ones, norm_bias=ones, out_dtype=bf16)),
+            "qwen3: x += d; y = norm(x)": gbs(tokens * hidden * (4 + 4 + 2 + 2),
+                                              lambda: ops.add_rmsnorm(x, delta, ones, 1e-6, bf16))}
+        # what follows a mixer's heads
+        H, D, V = memory
+        heads_out = torch.randn(tokens, H * V, device="cuda")
+        gate = torch.randn(tokens, H * V, device="cuda")
+        wide = torch.ones(H * V, device="cuda")
+        gate_up = torch.randn(tokens, 2 * H * V, device="cuda").to(bf16)
+        kernels[f"after_the_heads_{tokens}"] = {
+            "zitezen: per-head unit RMS, weight, sigmoid gate": gbs(
+                tokens * H * V * (4 + 4 + 2), lambda: ops.head_norm_gate(heads_out, wide, gate, H, 1e-5, bf16)),
+            "zitezen: relu(u)^2": gbs(tokens * H * V * 2 * 2, lambda: ops.relu_squared(gate_up[:, :H * V].contiguous())),
+            "qwen3: silu(gate) * up": gbs(tokens * H * V * 2 * 3, lambda: ops.silu_mul(gate_up))}
+    # one decode step of 8 requests: the recurrence's state against attention's cached keys and values
+    batch, context = 8, prompt
+    H, D, V = memory
+    width = 2 * H * D + 2 * H * V + 2 * H
+    proj = torch.randn(batch, width, device="cuda") * 0.1
+    state = torch.zeros(batch, ops.mlstm_state_values(H, D, V), device="cuda")
+    zeros = torch.zeros(H, device="cuda")
+    offsets = (0, H * D, 2 * H * D, 2 * H * D + 2 * H * V, 2 * H * D + 2 * H * V + H)
+    rows, ones_int = ints(list(range(batch))), ints([1] * batch)
+    kernels["decode_step_mixer_8_requests"] = {
+        "zitezen: recurrence, state read and written": gbs(
+            2 * state.numel() * 4, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, rows, ones_int, rows,
+                                                          H, D, V))}
+    pages = batch * (-(-context // 16))
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(batch, -1)
+    positions = ints([context - 1] * batch)
+    cache = torch.randn(pages, 2, kv_heads, 16, dim, device="cuda").to(bf16)
+    q = torch.randn(batch, heads, dim, device="cuda").to(bf16)
+    attended = torch.empty_like(q)
+    kv_bytes = cache.numel() * 2
+    kernels["decode_step_mixer_8_requests"]["qwen3: split-key attention over %d cached positions" % context] = gbs(
+        kv_bytes, lambda: ops.paged_attention_decode(q, cache, attended, table, rows, rows, positions, dim ** -0.5,
+                                                     context))
+    kernels["decode_step_mixer_8_requests"]["zitezen: the general kernel on the same rows, capped scores, a gate per head"] = gbs(
+        kv_bytes, lambda: ops.paged_attention_tile(q, cache, attended, table, rows, rows, ones_int, positions,
+                                                   dim ** -0.5, softcap=30.0, gate=q[:, :, 0].contiguous(),
+                                                   gate_per_head=True))
+    LH, LD, LR, LV, rank, _ = latent
+    shared = torch.randn(pages, 1, 1, 16, rank + LR, device="cuda").to(bf16)
+    lq = torch.randn(batch, LH, rank + LR, device="cuda").to(bf16)
+    mixed = torch.empty(batch, LH, rank, dtype=bf16, device="cuda")
+    kernels["decode_step_mixer_8_requests"]["zitezen: attention over the shared latent rows"] = gbs(
+        shared.numel() * 2, lambda: ops.paged_attention_tile(lq, shared, mixed, table, rows, rows, ones_int, positions,
+                                                             (LD + LR) ** -0.5))
+    # a prompt in one step
+    tokens = prompt
+    proj = torch.randn(tokens, width, device="cuda") * 0.1
+    state.zero_()
+    one_row, length = ints([0]), ints([tokens])
+    kernels[f"prompt_mixer_{tokens}"] = {
+        "zitezen: recurrence, token by token": tflops(
+            tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, one_row, length,
+                                                             one_row, H, D, V))}
+    pages = -(-tokens // 16)
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, -1)
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    cache = torch.randn(pages, 2, kv_heads, 16, dim, device="cuda").to(bf16)
+    q = torch.randn(tokens, heads, dim, device="cuda").to(bf16)
+    attended = torch.empty_like(q)
+    flops = 4.0 * dim * heads * tokens * (tokens + 1) / 2
+    tile = ops.flash_prefill_tile()
+    starts = list(range(0, tokens, tile))[::-1]
+    kernels[f"prompt_mixer_{tokens}"]["qwen3: tensor-core attention"] = tflops(
+        flops, lambda: ops.flash_prefill(q, cache, attended, table, ints([0] * len(starts)), ints(starts),
+                                         ints([min(tile, tokens - s) for s in starts]), positions, dim ** -0.5,
+                                         longest_context=tokens))
+    starts = list(range(0, tokens, 16))
+    kernels[f"prompt_mixer_{tokens}"]["zitezen: the general kernel, capped scores, a gate per head"] = tflops(
+        flops, lambda: ops.paged_attention_tile(q, cache, attended, table, ints([0] * len(starts)), ints(starts),
+                                                ints([min(16, tokens - s) for s in starts]), positions, dim ** -0.5,
+                                                softcap=30.0, gate=q[:, :, 0].contiguous(), gate_per_head=True))
+    shared = torch.randn(pages, 1, 1, 16, rank + LR, device="cuda").to(bf16)
+    lq = torch.randn(tokens, LH, rank + LR, device="cuda").to(bf16)
+    mixed = torch.empty(tokens, LH, rank, dtype=bf16, device="cuda")
+    kernels[f"prompt_mixer_{tokens}"]["zitezen: attention over the shared latent rows"] = tflops(
+        2.0 * (2 * rank + LR) * LH * tokens * (tokens + 1) / 2,
+        lambda: ops.paged_attention_tile(lq, shared, mixed, table, ints([0] * len(starts)), ints(starts),
+                                         ints([min(16, tokens - s) for s in starts]), positions, (LD + LR) ** -0.5))
+    ops.check_status("cuda")
+    out["kernels"] = kernels
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -903,7 +1098,7 @@ def main():
     parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
     parser.add_argument("--page-tokens", type=int, default=16, help="workloads: tokens per cache page")
     parser.add_argument("--max-context", type=int, default=0, help="workloads: the engine's context limit")
-    parser.add_argument("--design", choices=("mekazen",),
+    parser.add_argument("--design", choices=("mekazen", "zitezen"),
                         help="another decoder design beside Qwen3 at equal layer sizes, and its kernels beside their like")
     parser.add_argument("--chunk", type=int, default=0, help="--design: positions per chunk of the mask (0: the context)")
     parser.add_argument("--kernels-only", action="store_true",
@@ -919,6 +1114,8 @@ def main():
     if args.decode_resident is not None:
         from metallix_b200 import ops
         ops.set_decode_resident_blocks(args.decode_resident, max(args.decode_many, args.decode_resident))
+    if args.design == "zitezen" and not args.workload:
+        return design_zitezen(args)
     if args.design and not args.workload:
         return design(args)
     if args.workload:

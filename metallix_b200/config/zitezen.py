@@ -149,12 +149,13 @@ class LatentMixer:
                 f"{base}.uk": (h * self.dim, self.kv_rank), f"{base}.uv": (h * self.vdim, self.kv_rank),
                 f"{base}.o": (w, h * self.vdim)}
 
-    def part(self, base: str, w: int, eps: float) -> PartSpec:
+    def part(self, base: str, w: int, eps: float, cache_mode: str = "auto") -> PartSpec:
         position = None
         if self.rotary_dims:
             position = PartSpec("rope_interleaved", {"theta": self.rotary_base, "rotary_dim": self.rotary_dims,
                                                      "head_dim": self.rot_dim, "scaling": None})
         return PartSpec("latent_attention", {
+            "cache_mode": cache_mode,
             "hidden_size": w, "num_heads": self.heads, "head_dim": self.dim, "rotary_head_dim": self.rot_dim,
             "value_dim": self.vdim, "kv_rank": self.kv_rank, "q_rank": self.q_rank, "scale": self.scale, "eps": eps,
             "q_down_proj": f"{base}.dq", "q_up_proj": f"{base}.uq", "kv_down_proj": f"{base}.dkv",
@@ -352,7 +353,10 @@ class ZitezenConfig:
         return out
 
     # ------------------------------------------------------------- model spec
-    def to_model_spec(self) -> ModelSpec:
+    def to_model_spec(self, latent_cache: str = "auto") -> ModelSpec:
+        """``latent_cache``: what the latent attention keeps per position: "latent"
+        (the shared latent row), "heads" (every head's key and value rows) or
+        "auto" (the latter where the tensor-core kernels take the head size)."""
         w, eps, s = self.width, self.norm_eps, self.streams
         norm = lambda name: PartSpec("dynamic_tanh", {"size": w, "weight": name, "bias": f"{name}.b",
                                                       "alpha": f"{name}.alpha"})
@@ -369,7 +373,9 @@ class ZitezenConfig:
                     "up_proj": f"{base}.mlp.up", "down_proj": f"{base}.mlp.down"})
                 block["feed_forward"] = connection(base, 2)
             layers.append(LayerSpec(
-                name=base, block=PartSpec("hyper_connections", block), mixer=layer.mixer.part(f"{base}.mix", w, eps),
+                name=base, block=PartSpec("hyper_connections", block),
+                mixer=layer.mixer.part(f"{base}.mix", w, eps, latent_cache) if layer.kind == "latent_attention"
+                else layer.mixer.part(f"{base}.mix", w, eps),
                 feed_forward=feed_forward, mixer_norm=norm(f"{base}.norm1"),
                 feed_forward_norm=norm(f"{base}.norm2") if layer.ff else None))
         # every run of a layer, a repeated one too, keeps what it caches in an entry of its own

@@ -60,7 +60,7 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
                               int max_pages, const int* __restrict__ row_token,
                               const int* __restrict__ row_request, const int* __restrict__ positions,
                               int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                              int window, int chunk, float scale, int* status) {
+                              int window, int chunk, float scale, float softcap, int* status) {
   constexpr int E = Vec16<T>::kElems;  // elements per 16-byte piece
   constexpr int LPK = HD / E;          // 16-byte pieces (and lanes) per key row
   constexpr int KPW = 32 / LPK;        // key rows a warp reads at once
@@ -149,7 +149,7 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
 #pragma unroll
       for (int offset = LPK / 2; offset > 0; offset >>= 1)
         dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], offset);
-      if (sub == 0 && kk < count) s_score[h * kSplitKeys + kk] = dots[h] * scale;
+      if (sub == 0 && kk < count) s_score[h * kSplitKeys + kk] = capped_score(dots[h] * scale, softcap);
     }
   }
   __syncthreads();
@@ -253,7 +253,7 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
                                   int max_pages, const int* __restrict__ row_token,
                                   const int* __restrict__ row_request, const int* __restrict__ positions,
                                   int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                                  int window, int chunk, float scale, int* status) {
+                                  int window, int chunk, float scale, float softcap, int* status) {
   constexpr int ROW_BYTES = HD * 2;
   constexpr int TILE_BYTES = kSplitKeys * (ROW_BYTES + 16);
   extern __shared__ __align__(128) unsigned char mma_shared[];
@@ -365,14 +365,14 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
     }
   }
   // Row g of the tile is query head g; this thread holds keys nb * 8 + 2t, 2t + 1.
-  const float scale_log2 = scale * 1.4426950408889634f;
+  constexpr float kLog2E = 1.4426950408889634f;
   float m_w = -INFINITY;
 #pragma unroll
   for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int kk = key_base + nb * 8 + 2 * t + j;
-      sc[nb][j] = kk < count ? sc[nb][j] * scale_log2 : -INFINITY;
+      sc[nb][j] = kk < count ? capped_score(sc[nb][j] * scale, softcap) * kLog2E : -INFINITY;
       m_w = fmaxf(m_w, sc[nb][j]);
     }
   }
@@ -467,7 +467,7 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
                                   int max_pages, const int* __restrict__ row_token,
                                   const int* __restrict__ row_request, const int* __restrict__ positions,
                                   int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                                  int window, int chunk, float scale, int* status) {
+                                  int window, int chunk, float scale, float softcap, int* status) {
   constexpr int HALVES = HD / kTmaColumns;                 // 64-value halves of a row
   constexpr int TILE_BYTES = kSplitKeys * HD * 2;
   extern __shared__ unsigned char tma_decode_raw[];
@@ -569,14 +569,14 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
     }
   }
   // Row g of the tile is query head g; this thread holds keys nb * 8 + 2t, 2t + 1.
-  const float scale_log2 = scale * 1.4426950408889634f;
+  constexpr float kLog2E = 1.4426950408889634f;
   float m_w = -INFINITY;
 #pragma unroll
   for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int kk = key_base + nb * 8 + 2 * t + j;
-      sc[nb][j] = kk >= lo && kk <= hi ? sc[nb][j] * scale_log2 : -INFINITY;
+      sc[nb][j] = kk >= lo && kk <= hi ? capped_score(sc[nb][j] * scale, softcap) * kLog2E : -INFINITY;
       m_w = fmaxf(m_w, sc[nb][j]);
     }
   }
@@ -687,7 +687,7 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
                                        int max_pages, const int* __restrict__ row_token,
                                        const int* __restrict__ row_request, const int* __restrict__ positions,
                                        int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
-                                       int window, int chunk, float scale, int* status) {
+                                       int window, int chunk, float scale, float softcap, int* status) {
   constexpr int HALVES = HD / kTmaColumns;                 // 64-value halves of a row
   constexpr int TILE_BYTES = kSplitKeys * HD * 2;
   extern __shared__ unsigned char tma_decode_raw[];
@@ -771,7 +771,7 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
       qa2[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
     }
   }
-  const float scale_log2 = scale * 1.4426950408889634f;
+  constexpr float kLog2E = 1.4426950408889634f;
   const int key_base = warp * 32;
   float m_run = -INFINITY, l_run = 0.0f;   // of this warp's keys of all tiles so far, row g
   float o[HD / 8][4];
@@ -813,7 +813,7 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int kk = key_base + nb * 8 + 2 * t + j;
-        sc[nb][j] = kk >= lo && kk <= hi ? sc[nb][j] * scale_log2 : -INFINITY;
+        sc[nb][j] = kk >= lo && kk <= hi ? capped_score(sc[nb][j] * scale, softcap) * kLog2E : -INFINITY;
         m_t = fmaxf(m_t, sc[nb][j]);
       }
     }
@@ -1005,6 +1005,8 @@ struct DecodeProject {
   // values apart, in the type of q.
   const void* gate = nullptr;
   long long gate_stride = 0;
+  // A cap on the scaled scores ahead of the softmax (0: none).
+  float softcap = 0.0f;
 };
 
 template <typename T, int HD, int G>
@@ -1027,7 +1029,7 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   kernel<<<grid, kDecodeThreads, shared, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(cache), partial, block_tables, max_pages,
       row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk,
-      scale, status);
+      scale, project.softcap, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
@@ -1089,7 +1091,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
       if (attribute != cudaSuccess) return static_cast<int>(attribute);
       e = launch_chained(kernel, dim3(slots, kv_heads, rows), dim3(kDecodeThreads), shared, stream, map_cache,
                          static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
-                         positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status);
+                         positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, project.softcap, status);
       if (e != cudaSuccess) return static_cast<int>(e);
       return finish(slots);
     }
@@ -1098,7 +1100,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
     if (attribute != cudaSuccess) return static_cast<int>(attribute);
     e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream, map_cache,
                        static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
-                       positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status);
+                       positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, project.softcap, status);
   } else {
     const int shared = 2 * kSplitKeys * (HD * 2 + 16);
     auto kernel = paged_attention_decode_mma_kernel<HD>;
@@ -1107,7 +1109,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
     e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream,
                        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
                        partial, block_tables, max_pages, row_token, row_request, positions, heads,
-                       kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status);
+                       kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, project.softcap, status);
   }
   if (e != cudaSuccess) return static_cast<int>(e);
   return finish(0);
@@ -1147,15 +1149,16 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
                                        const int* row_request, const int* positions, int rows,
                                        int heads, int kv_heads, int head_dim, int page_tokens,
                                        int num_pages, int max_splits, int window, int chunk, float scale,
-                                       int dtype, const void* gate, long long gate_stride, int* status,
+                                       int dtype, const void* gate, long long gate_stride, float softcap, int* status,
                                        cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) || max_splits <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const int group = heads / kv_heads;
-  DecodeProject project;   // no projection here; the gate, if any
+  DecodeProject project;   // no projection here; the gate and the cap on the scores, if any
   project.gate = gate;
   project.gate_stride = gate_stride;
+  project.softcap = softcap;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
 #define BY_GROUP(T, HD)                                        \
@@ -1194,7 +1197,7 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
                                                int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                                int max_splits, int window, int chunk, float scale, const void* w, long long ldw,
                                                int hidden, float* summands, const void* gate, long long gate_stride,
-                                               int* status, cudaStream_t stream) {
+                                               float softcap, int* status, cudaStream_t stream) {
   if (rows <= 0 || hidden <= 0 || max_splits <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_paged_attention_decode_project_supported(head_dim, heads, kv_heads, kBF16, tokens, w, ldw))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -1206,6 +1209,7 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
   project.summands = summands;
   project.gate = gate;
   project.gate_stride = gate_stride;
+  project.softcap = softcap;
   void* out = nullptr;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
@@ -1277,7 +1281,7 @@ MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache,
   if (e != cudaSuccess) return static_cast<int>(e);
   return mxb_paged_attention_decode(q, cache, out, scratch, block_tables, max_pages, row_token,
                                     row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
-                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, status, stream);
+                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, 0.0f, status, stream);
 }
 
 MXB_TIMELINE_EXPORT(mxb_timeline_attention)

@@ -73,7 +73,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                      const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                      const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
-                     int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale,
+                     int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, float softcap,
                      const __nv_bfloat16* __restrict__ gate, long long gate_stride, int* status) {
   constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
   constexpr int TILE_BYTES = kFlashKeys * HD * 2;
@@ -189,6 +189,16 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       }
     }
 
+    // ---- a cap on the scaled scores, if any: c tanh(s scale / c), kept over scale so
+    // that what follows multiplies by scale as before.
+    if (softcap > 0.0f) {
+      const float inner = scale / softcap, outer = softcap / scale;
+#pragma unroll
+      for (int nb = 0; nb < kFlashKeys / 8; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[nb][j] = outer * tanhf(s[nb][j] * inner);
+      }
+    }
     // ---- mask, running maximum and sum (float32). m_* hold the running
     // maximum already multiplied by scale * log2(e).
     const int key0 = kt * kFlashKeys;
@@ -290,7 +300,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
                         const int* tile_request, const int* tile_start, const int* tile_length,
                         const int* positions, int tiles, int heads, int kv_heads, int page_tokens,
                         int num_pages, int window, int chunk, float scale, const void* gate, long long gate_stride,
-                        int* status, cudaStream_t stream) {
+                        float softcap, int* status, cudaStream_t stream) {
   const int shared = 4 * kFlashKeys * HD * 2;
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
@@ -299,7 +309,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
   kernel<<<grid, kFlashThreads, shared, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,
-      positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
+      positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, softcap,
       static_cast<const __nv_bfloat16*>(gate), gate_stride, status);
   return static_cast<int>(cudaGetLastError());
 }
@@ -322,15 +332,15 @@ MXB_API int mxb_flash_prefill(const void* q, const void* cache, void* out, const
                               int max_pages, const int* tile_request, const int* tile_start,
                               const int* tile_length, const int* positions, int tiles, int heads,
                               int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
-                              float scale, int dtype, const void* gate, long long gate_stride, int* status,
-                              cudaStream_t stream) {
+                              float scale, int dtype, const void* gate, long long gate_stride, float softcap,
+                              int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (!mxb_flash_prefill_supported(head_dim, heads, kv_heads, dtype)) return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, status,
+                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, status,
                             stream);
   return launch_flash<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, status,
+                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, status,
                             stream);
 }

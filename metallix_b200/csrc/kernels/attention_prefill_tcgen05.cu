@@ -75,7 +75,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                              const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                              const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
-                             int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale,
+                             int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, float softcap,
                              int shared_bytes, float* __restrict__ partial, const __nv_bfloat16* __restrict__ gate,
                              long long gate_stride, int* status) {
   using Config = FaConfig<HD>;
@@ -330,6 +330,11 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       uint32_t raw[PART_KEYS];
       tc_load_32(tmem_s, raw);
       float s[PART_KEYS];
+      if (softcap > 0.0f) {   // c tanh(s scale / c), kept over scale so that what follows multiplies by scale as before
+        const float inner = scale / softcap, outer = softcap / scale;
+#pragma unroll
+        for (int j = 0; j < PART_KEYS; ++j) raw[j] = __float_as_uint(outer * tanhf(__uint_as_float(raw[j]) * inner));
+      }
       if (all_seen) {
 #pragma unroll
         for (int j = 0; j < PART_KEYS; ++j) s[j] = __uint_as_float(raw[j]);
@@ -472,7 +477,7 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
                            const int* tile_request, const int* tile_start, const int* tile_length,
                            const int* positions, int tokens, int tiles, int heads, int kv_heads, int page_tokens,
                            int num_pages, int window, int chunk, float scale, int key_shares, float* partial,
-                           const void* gate, long long gate_stride, int* status, cudaStream_t stream) {
+                           const void* gate, long long gate_stride, float softcap, int* status, cudaStream_t stream) {
   using Config = FaConfig<HD>;
   CUtensorMap map_q, map_cache;
   // q as [tokens, heads * HD]; the cache as [pages * 2 * kv_heads * page_tokens, HD].
@@ -495,7 +500,7 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
   dim3 grid(heads, tiles, shared_out ? key_shares : 1);
   kernel<<<grid, kFaThreads, shared_bytes, stream>>>(
       map_q, map_cache, static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start,
-      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, shared_bytes,
+      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, softcap, shared_bytes,
       shared_out ? partial : nullptr, static_cast<const __nv_bfloat16*>(gate), gate_stride, status);
   e = cudaGetLastError();
   if (e != cudaSuccess || !shared_out) return static_cast<int>(e);
@@ -528,7 +533,8 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
                                       const int* tile_length, const int* positions, int tokens, int tiles,
                                       int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                       int window, int chunk, float scale, int dtype, int key_shares, float* partial,
-                                      const void* gate, long long gate_stride, int* status, cudaStream_t stream) {
+                                      const void* gate, long long gate_stride, float softcap, int* status,
+                                      cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (key_shares < 1 || key_shares > kMergeShares || (key_shares > 1 && partial == nullptr))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -540,8 +546,8 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
   if (head_dim == 64)
     return launch_flash_tc<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                                positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
-                               key_shares, partial, gate, gate_stride, status, stream);
+                               key_shares, partial, gate, gate_stride, softcap, status, stream);
   return launch_flash_tc<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                               positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
-                              key_shares, partial, gate, gate_stride, status, stream);
+                              key_shares, partial, gate, gate_stride, softcap, status, stream);
 }

@@ -70,6 +70,10 @@ __device__ __forceinline__ void prefetch_line(const void* p) { asm volatile("pre
 // sigmoid(gate[token * gate_stride + head * head_dim + d]), in float32.
 __device__ __forceinline__ float sigmoid_of(float g) { return 1.0f / (1.0f + expf(-g)); }
 
+// A cap c on a scaled score ahead of the softmax: s <- c tanh(s / c), which keeps small scores and
+// bounds all of them to (-c, c); c = 0 leaves the score as it is.
+__device__ __forceinline__ float capped_score(float s, float cap) { return cap > 0.0f ? cap * tanhf(s / cap) : s; }
+
 // The first key a query at position `pos` sees. Two rules, either or both:
 // a sliding window keeps the last `window` positions (keys > pos - window), a
 // chunked mask keeps the keys of the query's own chunk of `chunk` positions,

@@ -40,7 +40,7 @@ __global__ void latent_cache_kernel(const T* __restrict__ x, long long ld, const
                                     int num_pages, int* status) {
   __shared__ float scratch[33];
   const int t = blockIdx.x;
-  const int slot = slots[t];
+  const int slot = slots != nullptr ? slots[t] : t;   // without slots: row t of a plain [tokens, rank + rot] buffer
   if (slot < 0) return;   // a padding row of a captured step
   const int pos = positions[t];
   if (slot >= num_pages * page_tokens || pos < 0 || (rotary_dim > 0 && pos >= table_positions)) {
@@ -85,9 +85,83 @@ __global__ void rotate_into_kernel(const T* __restrict__ src, long long ld_src, 
   }
 }
 
+// The other way to cache the same attention: per head, whole key and value rows. For every token, head h:
+//   q_heads[t, h] = [q_u (D) | rot(q_r) (R) | 0 ...]                       (width `hd`)
+//   K row at the token's slot = [k_h (D) | rotated shared key part (R) | 0 ...]
+//   V row                      = [v_h (V) | 0 ...]
+// q: [tokens, heads * (D + R)] with the rotated part still unrotated; up: [tokens, heads * D + heads * V], the
+// keys then the values that the latent was widened to; shared: [tokens, ...] holding the ALREADY rotated shared
+// key part from column shared_off on. The pool is [pages, 2, heads, page_tokens, hd].
+template <typename T>
+__global__ void latent_heads_kernel(const T* __restrict__ q, long long ld_q, const T* __restrict__ up, long long ld_up,
+                                    const T* __restrict__ shared_part, long long ld_shared, int shared_off,
+                                    T* __restrict__ q_heads, T* __restrict__ cache, const int* __restrict__ slots,
+                                    const int* __restrict__ positions, const float* __restrict__ cos_table,
+                                    const float* __restrict__ sin_table, int table_positions, int rotary_dim,
+                                    int interleaved, int heads, int D, int R, int V, int hd, int page_tokens,
+                                    int num_pages, int* status) {
+  const int t = blockIdx.x;
+  int pos = positions[t];
+  if (pos < 0 || (rotary_dim > 0 && pos >= table_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+    pos = 0;
+  }
+  const float* cos_row = cos_table + static_cast<long long>(pos) * (rotary_dim / 2);
+  const float* sin_row = sin_table + static_cast<long long>(pos) * (rotary_dim / 2);
+  const T* q_row = q + static_cast<long long>(t) * ld_q;
+  for (int e = threadIdx.x; e < heads * hd; e += blockDim.x) {
+    const int h = e / hd, i = e - h * hd;
+    float v = 0.0f;
+    if (i < D) v = to_float(q_row[h * (D + R) + i]);
+    else if (i < D + R) v = rotated_value(q_row + h * (D + R) + D, i - D, rotary_dim, interleaved, cos_row, sin_row);
+    q_heads[static_cast<long long>(t) * heads * hd + e] = from_float<T>(v);
+  }
+  const int slot = slots != nullptr ? slots[t] : -1;
+  if (slot < 0) return;
+  if (slot >= num_pages * page_tokens) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+    return;
+  }
+  const int page = slot / page_tokens, in_page = slot - page * page_tokens;
+  const T* up_row = up + static_cast<long long>(t) * ld_up;
+  const T* shared_row = shared_part + static_cast<long long>(t) * ld_shared + shared_off;
+  for (int e = threadIdx.x; e < heads * hd; e += blockDim.x) {
+    const int h = e / hd, i = e - h * hd;
+    T key = from_float<T>(0.0f), value = from_float<T>(0.0f);
+    if (i < D) key = up_row[h * D + i];
+    else if (i < D + R) key = shared_row[i - D];
+    if (i < V) value = up_row[heads * D + h * V + i];
+    const long long at = ((static_cast<long long>(page) * 2 * heads + h) * page_tokens + in_page) * hd + i;
+    cache[at] = key;
+    cache[at + static_cast<long long>(heads) * page_tokens * hd] = value;
+  }
+}
+
 }  // namespace mxb
 
 using namespace mxb;
+
+MXB_API int mxb_latent_heads(const void* q, long long ld_q, const void* up, long long ld_up, const void* shared_part,
+                             long long ld_shared, int shared_off, void* q_heads, void* cache, const int* slots,
+                             const int* positions, const float* cos_table, const float* sin_table, int table_positions,
+                             int rotary_dim, int interleaved, int heads, int D, int R, int V, int hd, int page_tokens,
+                             int num_pages, int tokens, int dtype, int* status, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads <= 0 || D + R > hd || V > hd || rotary_dim > R || rotary_dim % 2) return static_cast<int>(cudaErrorInvalidValue);
+  if (dtype == kF32)
+    latent_heads_kernel<float><<<tokens, 256, 0, stream>>>(
+        static_cast<const float*>(q), ld_q, static_cast<const float*>(up), ld_up, static_cast<const float*>(shared_part),
+        ld_shared, shared_off, static_cast<float*>(q_heads), static_cast<float*>(cache), slots, positions, cos_table,
+        sin_table, table_positions, rotary_dim, interleaved, heads, D, R, V, hd, page_tokens, num_pages, status);
+  else if (dtype == kBF16)
+    latent_heads_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(q), ld_q, static_cast<const __nv_bfloat16*>(up), ld_up,
+        static_cast<const __nv_bfloat16*>(shared_part), ld_shared, shared_off, static_cast<__nv_bfloat16*>(q_heads),
+        static_cast<__nv_bfloat16*>(cache), slots, positions, cos_table, sin_table, table_positions, rotary_dim,
+        interleaved, heads, D, R, V, hd, page_tokens, num_pages, status);
+  else return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(cudaGetLastError());
+}
 
 MXB_API int mxb_latent_cache(const void* x, long long ld, const float* w, float eps, int rank, int rot, int rotary_dim,
                              int interleaved, const float* cos_table, const float* sin_table, int table_positions,

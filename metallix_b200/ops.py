@@ -44,24 +44,26 @@ _SIGNATURES = {
                        _P, _P],
     "mxb_head_norm_gate": [_P, _P, _P, _L, _I, _P, _I, _I, _I, _I, _F, _P],
     "mxb_latent_cache": [_P, _L, _P, _F, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "mxb_latent_heads": [_P, _L, _P, _L, _P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                         _I, _P, _P],
     "mxb_rotate_into": [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P, _P],
     "mxb_relu_squared": [_P, _P, _L, _I, _P],
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                   _F, _I, _P, _L, _P, _P],
+                                   _F, _I, _P, _L, _F, _P, _P],
     "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
     "mxb_sigmoid_gate": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _P],
     "mxb_softcap": [_P, _F, _L, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_decode_project_supported": [_I, _I, _I, _I, _I, _P, _L],
     "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                           _F, _P, _L, _I, _P, _P, _L, _P, _P],
+                                           _F, _P, _L, _I, _P, _P, _L, _F, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
-    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _L, _P, _P],
+    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _L, _F, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
     "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
-                                  _P, _L, _P, _P],
+                                  _P, _L, _F, _P, _P],
     "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
     "mxb_flash_prefill_tcgen05_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
@@ -516,29 +518,75 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.T
 
 
 # ------------------------------------------------- attention through a latent
-def latent_cache(x: torch.Tensor, weight: torch.Tensor, eps: float, rank: int, cache: torch.Tensor,
-                 slots: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
-                 sin: Optional[torch.Tensor], interleaved: bool) -> None:
+def latent_cache(x: torch.Tensor, weight: torch.Tensor, eps: float, rank: int, cache: Optional[torch.Tensor],
+                 slots: Optional[torch.Tensor], positions: torch.Tensor, cos: Optional[torch.Tensor],
+                 sin: Optional[torch.Tensor], interleaved: bool) -> Optional[torch.Tensor]:
     """x ``[tokens, rank + rot]`` (rows may be strided): the first ``rank``
     values are RMS-normed with ``weight``, the rest rotated by the positions,
     and both stored at ``slots`` of the one-plane pool
-    ``[pages, 1, 1, page_tokens, rank + rot]``."""
+    ``[pages, 1, 1, page_tokens, rank + rot]``. Without a cache the rows are
+    returned instead, ``[tokens, rank + rot]``."""
     _need(x.is_cuda and x.dtype in _CODES and x.dim() == 2 and x.stride(1) == 1, "x must be [tokens, rank + rot]")
+    tokens = x.shape[0]
+    rows = None
+    if cache is None:
+        _need(slots is None, "slots need a cache")
+        rows = torch.empty((tokens, x.shape[1]), dtype=x.dtype, device=x.device)
+        cache = rows.view(tokens, 1, 1, 1, x.shape[1])
     _check(cache, "cache", (x.dtype,), 5)
     num_pages, planes, kv_heads, page_tokens, width = cache.shape
     _need(planes == 1 and kv_heads == 1 and width == x.shape[1] and 0 < rank <= width,
           "cache must be [pages, 1, 1, page_tokens, rank + rot]")
     _check(weight, "weight", (torch.float32,), 1)
     _need(weight.numel() == rank, "the latent's norm weight has the wrong size")
-    tokens = x.shape[0]
-    _check(slots, "slots", (torch.int32,), 1)
+    if rows is None:
+        _check(slots, "slots", (torch.int32,), 1)
+        _need(slots.numel() == tokens, "one slot per token")
     _check(positions, "positions", (torch.int32,), 1)
-    _need(slots.numel() == tokens and positions.numel() == tokens, "one slot and one position per token")
+    _need(positions.numel() == tokens, "one position per token")
     rotary_dim, table_positions = _tables(cos, sin, width - rank)
     _call("mxb_latent_cache", x.data_ptr(), x.stride(0), weight.data_ptr(), float(eps), rank, width - rank, rotary_dim,
-          1 if interleaved else 0, _ptr(cos), _ptr(sin), table_positions, positions.data_ptr(), slots.data_ptr(),
+          1 if interleaved else 0, _ptr(cos), _ptr(sin), table_positions, positions.data_ptr(), _ptr(slots),
           cache.data_ptr(), page_tokens, num_pages, tokens, _CODES[x.dtype], status_word(x.device).data_ptr(),
           _stream())
+    return rows
+
+
+def latent_heads(q: torch.Tensor, up: torch.Tensor, shared: torch.Tensor, shared_off: int, q_heads: torch.Tensor,
+                 cache: Optional[torch.Tensor], slots: Optional[torch.Tensor], positions: torch.Tensor,
+                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool, dim: int, rot: int,
+                 vdim: int) -> None:
+    """Whole key and value rows per head from what a latent was widened to.
+    ``q`` ``[tokens, heads * (dim + rot)]`` (its rotated parts not yet rotated),
+    ``up`` ``[tokens, heads * dim + heads * vdim]`` (every head's unrotated key
+    part, then every head's values), ``shared[:, shared_off:shared_off + rot]``
+    the already rotated key part all heads share. Writes ``q_heads``
+    ``[tokens, heads, hd]`` = [q_u | rot(q_r) | 0] and, at ``slots`` of
+    ``cache`` ``[pages, 2, heads, page_tokens, hd]``, K = [k_h | shared | 0]
+    and V = [v_h | 0]."""
+    dtype = q.dtype
+    for name, tensor in (("q", q), ("up", up), ("shared", shared)):
+        _need(tensor.is_cuda and tensor.dtype == dtype and tensor.dtype in _CODES and tensor.dim() == 2
+              and tensor.stride(1) == 1, f"{name} must be a CUDA [tokens, columns] tensor with unit column stride")
+    _check(q_heads, "q_heads", (dtype,), 3)
+    tokens, heads, hd = q_heads.shape
+    _need(q.shape == (tokens, heads * (dim + rot)) and up.shape == (tokens, heads * (dim + vdim))
+          and shared.shape[0] == tokens and shared_off + rot <= shared.shape[1] and dim + rot <= hd and vdim <= hd,
+          "q, up, shared and q_heads do not fit the head layout")
+    num_pages, page_tokens = 0, 1
+    if cache is not None:
+        _check(cache, "cache", (dtype,), 5)
+        _need(cache.shape[1] == 2 and cache.shape[2] == heads and cache.shape[4] == hd,
+              "cache must be [pages, 2, heads, page_tokens, hd]")
+        num_pages, page_tokens = cache.shape[0], cache.shape[3]
+        _check(slots, "slots", (torch.int32,), 1)
+        _need(slots.numel() == tokens, "one slot per token")
+    _check(positions, "positions", (torch.int32,), 1)
+    rotary_dim, table_positions = _tables(cos, sin, rot)
+    _call("mxb_latent_heads", q.data_ptr(), q.stride(0), up.data_ptr(), up.stride(0), shared.data_ptr(), shared.stride(0),
+          shared_off, q_heads.data_ptr(), _ptr(cache), _ptr(slots) if cache is not None else None, positions.data_ptr(),
+          _ptr(cos), _ptr(sin), table_positions, rotary_dim, 1 if interleaved else 0, heads, dim, rot, vdim, hd,
+          page_tokens, num_pages, tokens, _CODES[dtype], status_word(q.device).data_ptr(), _stream())
 
 
 def _tables(cos, sin, width: int):
@@ -764,14 +812,17 @@ def flash_key_shares(blocks: int, longest_context: int, window: int = 0, chunk: 
 def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
                   positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto",
-                  longest_context: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  longest_context: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None,
+                  softcap: float = 0.0) -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
     float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
     of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
     warp-level kernel) or "auto" (tcgen05 where it takes the page size).
     ``longest_context`` (the most keys any of the tiles sees, 0: unknown)
     lets the tcgen05 kernel share a tile's keys out among several blocks when
-    the tiles alone would leave most of the GPU idle."""
+    the tiles alone would leave most of the GPU idle. ``softcap`` c: scores
+    pass c tanh(s / c) ahead of the softmax."""
+    _need(softcap >= 0.0, "the cap on the scores cannot be negative")
     _check(q, "q", (torch.bfloat16,), 3)
     _check(out, "out", (torch.bfloat16,), 3)
     _check(cache, "cache", (torch.bfloat16,), 5)
@@ -807,7 +858,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
               block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
               tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
               page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
-              _ptr(gate), gate_stride, status_word(q.device).data_ptr(), _stream())
+              _ptr(gate), gate_stride, float(softcap), status_word(q.device).data_ptr(), _stream())
         if shares > 1:
             global _launches
             _launches += 1   # the kernel that puts the shares together
@@ -815,7 +866,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     _call("mxb_flash_prefill", q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
           positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,
-          int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], _ptr(gate), gate_stride,
+          int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], _ptr(gate), gate_stride, float(softcap),
           status_word(q.device).data_ptr(), _stream())
     return out
 
@@ -847,7 +898,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
                            row_request: torch.Tensor, positions: torch.Tensor, scale: float,
                            longest_context: int, window: int = 0,
                            partial: Optional[torch.Tensor] = None, chunk: int = 0,
-                           gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
     """Attention of single tokens over their requests' cached keys, split
     along the keys. ``row_token[i]`` is the token (row of q and out) of the
     i-th decoded request, negative for a padding row; ``row_request[i]`` its
@@ -855,8 +906,10 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
     fixes the number of splits. ``partial`` is float32 scratch of
     rows * heads * splits * (head_dim + 2) values, allocated here if absent.
     ``gate`` ([tokens, heads * head_dim] in q's type, rows may be strided):
-    the output is multiplied by sigmoid(gate) as it is written."""
+    the output is multiplied by sigmoid(gate) as it is written. ``softcap`` c:
+    scores pass c tanh(s / c) ahead of the softmax."""
     dtype = q.dtype
+    _need(softcap >= 0.0, "the cap on the scores cannot be negative")
     _check(q, "q", tuple(_CODES), 3)
     _check(out, "out", (dtype,), 3)
     _check(cache, "cache", (dtype,), 5)
@@ -881,7 +934,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
     _call("mxb_paged_attention_decode", q.data_ptr(), cache.data_ptr(), out.data_ptr(), partial.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
-          int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], _ptr(gate), gate_stride,
+          int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], _ptr(gate), gate_stride, float(softcap),
           status_word(q.device).data_ptr(), _stream())
     return out
 
@@ -910,7 +963,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
                                    row_token: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor,
                                    scale: float, longest_context: int, weight: torch.Tensor,
                                    window: int = 0, chunk: int = 0,
-                                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                                   gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
     """``paged_attention_decode`` followed at once by the output projection
     ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 64 tokens in
     bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
@@ -938,7 +991,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, tokens, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), int(chunk or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
-          _ptr(gate), gate_stride,
+          _ptr(gate), gate_stride, float(softcap),
           status_word(q.device).data_ptr(), _stream())
     return summands
 

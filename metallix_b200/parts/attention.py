@@ -16,8 +16,9 @@ output projection (``gate_scope="head"``: Wg has one row per head, and a
 head's whole output is multiplied by one number); ``softcap`` c bounds the
 scores, s <- c tanh(s / c), ahead of the softmax; ``value_dim`` lets the
 values be wider or narrower than the keys (a page then holds rows as wide as
-the wider of the two, the others padded with zeros). A score cap, a per-head
-gate or values of another width run on the general kernel only.
+the wider of the two, the others padded with zeros). Values of another width
+than the keys run on the general kernel only; a per-head gate is spread over
+the head's values for the tensor-core kernels.
 
 Every size and constant is a parameter. When the head norms are RMSNorms (or
 absent) and the position encoding offers cos/sin tables (or is absent), norm,
@@ -127,6 +128,54 @@ def tiles_of(ctx: StepContext) -> Dict[str, object]:
     return tiles
 
 
+def attend_cached(q_heads: torch.Tensor, cache: CacheView, ctx: StepContext, *, scale: float, window: int = 0,
+                  chunk: int = 0, softcap: float = 0.0, gate: Optional[torch.Tensor] = None, gate_per_head: bool = False,
+                  split_decode: bool = False, flash: bool = False, project=None):
+    """Attention of a step's queries ``[tokens, heads, head_dim]`` over what the
+    cache entry holds (this step's rows included), each kind of request on the
+    kernel made for it: single tokens split along the keys, portions of prompts
+    on the tensor cores in tiles of 128, whatever is left (and everything, where
+    those kernels do not take the head layout or the type) on the general
+    kernel. Returns (``[tokens, heads, head_dim]``, False); with ``project`` (the
+    output projection, a ``Linear``) a step of few single tokens may come back
+    as (float32 ``[heads, tokens, hidden]`` summands, True), merged and
+    projected by one kernel."""
+    tokens, heads, head_dim = q_heads.shape
+    tiles = tiles_of(ctx)
+    multi_tiles = tiles["multi_tiles"]
+    split = tiles["decode_rows"] and split_decode
+    kv_heads = cache.pool.shape[2]
+    # The gate, if any, rides in whichever kernel writes a token's output.
+    if (project is not None and split and multi_tiles == 0 and tokens <= PROJECT_TOKENS and project.rows_are_short()
+            and ops.decode_project_supported(head_dim, heads, kv_heads, q_heads.dtype, tokens, project.weight)):
+        # Only single tokens, at most 64 of them: the splits are merged
+        # and projected by one kernel, one summand per head.
+        return ops.paged_attention_decode_project(
+            q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
+            ctx.positions, scale, tiles["longest_context"], project.weight, window, chunk, gate=gate,
+            softcap=softcap), True
+    out = torch.empty_like(q_heads)
+    if split:
+        # Requests that bring one token: split along the keys.
+        ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],
+                                   tiles["decode_request"], ctx.positions, scale, tiles["longest_context"], window,
+                                   chunk=chunk, gate=gate, softcap=softcap)
+    if flash:
+        # Requests that bring several tokens: tensor cores, tiles of 128.
+        if tiles["wide_request"].numel():
+            ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, tiles["wide_request"],
+                              tiles["wide_start"], tiles["wide_length"], ctx.positions, scale, window,
+                              longest_context=tiles["longest_keys"], chunk=chunk, gate=gate, softcap=softcap)
+        rest = None if split else slice(multi_tiles, None)   # single tokens not yet served
+    else:
+        rest = slice(0, multi_tiles) if split else slice(0, None)
+    if rest is not None and tiles["tile_request"][rest].numel():
+        ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, tiles["tile_request"][rest],
+                                 tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
+                                 scale, window, chunk, gate=gate, softcap=softcap, gate_per_head=gate_per_head)
+    return out, False
+
+
 class GQAttention:
     kind = "gqa_attention"
     graph_safe = True  # launches the same kernels whatever the step's integers are
@@ -196,9 +245,8 @@ class GQAttention:
         eps_agree = (self.q_norm is None or self.k_norm is None or self.q_norm.eps == self.k_norm.eps)
         position_fuses = self.position is None or getattr(self.position, "fused_tables", False)
         self.dtype = runtime.dtype
-        # What only the general kernel does: a cap on the scores, one gate per
-        # head, values of another width than the keys.
-        self.general_only = bool(self.softcap) or self.gate_scope == "head" or self.value_dim != self.head_dim
+        # What only the general kernel does: values of another width than the keys.
+        self.general_only = self.value_dim != self.head_dim
         self.fused = norms_fuse and eps_agree and position_fuses and self.value_dim == self.head_dim
         self.split_decode = not self.general_only and ops.decode_attention_supported(
             self.head_dim, self.num_heads, self.num_kv_heads, self.dtype)
@@ -264,41 +312,17 @@ class GQAttention:
                 q_heads = q.contiguous().view(tokens, self.num_heads, self.head_dim)
             if write:
                 ops.write_cache(k, v, cache.pool, cache.slots, ctx.positions)
-        tiles = self._tiles(ctx)
-        multi_tiles = tiles["multi_tiles"]
-        split = tiles["decode_rows"] and self.split_decode
-        # The gate, if any, rides in whichever kernel writes a token's output.
-        if (summands and split and multi_tiles == 0 and tokens <= PROJECT_TOKENS and self.o.rows_are_short()
-                and ops.decode_project_supported(self.head_dim, self.num_heads, self.num_kv_heads, self.dtype,
-                                                 tokens, self.o.weight)):
-            # Only single tokens, at most 64 of them: the splits are merged
-            # and projected by one kernel, one summand per head.
-            return ops.paged_attention_decode_project(
-                q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
-                ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window, self.chunk,
-                gate=gate)
-        out = torch.empty_like(q_heads)
-        if split:
-            # Requests that bring one token: split along the keys.
-            ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],
-                                       tiles["decode_request"], ctx.positions, self.scale,
-                                       tiles["longest_context"], self.window, chunk=self.chunk,
-                                       gate=gate)
-        if self.flash:
-            # Requests that bring several tokens: tensor cores, tiles of 128.
-            if tiles["wide_request"].numel():
-                ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, tiles["wide_request"],
-                                  tiles["wide_start"], tiles["wide_length"], ctx.positions, self.scale,
-                                  self.window, longest_context=tiles["longest_keys"], chunk=self.chunk, gate=gate)
-            rest = None if split else slice(multi_tiles, None)   # single tokens not yet served
+        if self.gate_scope == "head" and gate is not None and (self.split_decode or self.flash):
+            # the tensor-core kernels take one gate per value: a head's number is spread over its values
+            gate = gate.unsqueeze(2).expand(tokens, self.num_heads, self.head_dim).reshape(tokens, self.q_size)
+            per_head_gate = False
         else:
-            rest = slice(0, multi_tiles) if split else slice(0, None)
-        if rest is not None and tiles["tile_request"][rest].numel():
-            ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, tiles["tile_request"][rest],
-                                     tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
-                                     self.scale, self.window, self.chunk, gate=gate, softcap=self.softcap,
-                                     gate_per_head=self.gate_scope == "head")
-        return self.o.forward(out.view(tokens, self.q_size))
+            per_head_gate = self.gate_scope == "head"
+        out, projected = attend_cached(
+            q_heads, cache, ctx, scale=self.scale, window=self.window, chunk=self.chunk, softcap=self.softcap, gate=gate,
+            gate_per_head=per_head_gate, split_decode=self.split_decode, flash=self.flash,
+            project=self.o if summands else None)
+        return out if projected else self.o.forward(out.view(tokens, self.q_size))
 
     def _attend_unequal(self, x, q, k, v, gate, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         """Values wider or narrower than the keys: a cached row is as wide as

@@ -15,7 +15,16 @@ q_u . (Wuk_h c) = (Wuk_h^T q_u) . c, and sum_j p_j Wuv_h c_j = Wuv_h (sum_j p_j 
 So a head's query against the cache is [Wuk_h^T q_u | rot(q_r)] (r + R values),
 its output a mixture of latents (r values) that Wuv_h widens to V afterwards:
 attention with H query heads over one shared key/value head, whatever the
-context's length.
+context's length. That is ``cache_mode="latent"``: the least memory, on the
+general attention kernel.
+
+``cache_mode="heads"`` keeps the equations in their first order instead: every
+position's latent is widened once, when it arrives, to each head's key
+[k_h | rot(kr)] and value v_h, and those rows are cached per head (padded
+with zeros to a head size the tensor-core kernels take: 64, 128 or 256). The
+cache is H (D + R + V) / (r + R) times as large; prompts and decode steps then
+run on the same kernels as grouped-query attention. ``"auto"`` takes the
+per-head rows where such a head size exists (keys and values up to 256 wide).
 """
 from __future__ import annotations
 
@@ -23,7 +32,7 @@ import torch
 
 from .. import ops
 from ..config.spec import CacheNeed, PartSpec
-from .attention import attention_tiles, tiles_of
+from .attention import attend_cached, attention_tiles, tiles_of
 from .linear import Linear
 from .registry import CacheView, Runtime, StepContext, WeightStore, build_part, register_part
 
@@ -63,8 +72,29 @@ class LatentAttention:
         self.o = Linear(matrix("o_proj", (hidden, H * V)), runtime)
         self.position = build_part("position", spec.get("position"), weights, runtime)
         self.dtype = runtime.dtype
+        mode = spec.get("cache_mode") or "auto"
+        if mode not in ("auto", "latent", "heads"):
+            raise ValueError(f"cache_mode must be 'auto', 'latent' or 'heads', got {mode!r}")
+        widest = max(D + R, V)
+        self.head_size = next((size for size in (64, 128, 256) if size >= widest), 0)
+        if mode == "heads" and not self.head_size:
+            raise ValueError(f"keys of {D + R} and values of {V} do not fit a head of up to 256 values")
+        self.per_head = mode == "heads" or (mode == "auto" and bool(self.head_size))
+        if self.per_head:
+            hd = self.head_size
+            # keys and values from the latent in one product: rows of uk, then rows of uv
+            self.kv_up = Linear.stacked([self.uk.reshape(H * D, self.rank), self.uv.reshape(H * V, self.rank)], runtime)
+            if V != hd:   # the output projection over padded heads: zero columns where the padding is
+                padded = torch.zeros((hidden, H, hd), dtype=self.o.weight.dtype, device=self.o.weight.device)
+                padded[:, :, :V] = self.o.weight.view(hidden, H, V)
+                self.o = Linear(padded.view(hidden, H * hd), runtime)
+            self.uk = self.uk_t = self.uv = None
+            self.split_decode = ops.decode_attention_supported(hd, H, H, self.dtype)
+            self.flash = ops.flash_prefill_supported(hd, H, H, self.dtype)
 
     def cache_need(self) -> CacheNeed:
+        if self.per_head:
+            return CacheNeed(kind="kv_pages", kv_heads=self.heads, head_dim=self.head_size)
         return CacheNeed(kind="kv_pages", kv_heads=1, head_dim=self.width, planes=1)
 
     def parts(self):
@@ -75,6 +105,8 @@ class LatentAttention:
         cos = self.position.cos if self.position is not None else None
         sin = self.position.sin if self.position is not None else None
         paired = bool(getattr(self.position, "interleaved", False))
+        if self.per_head:
+            return self._forward_per_head(x, ctx, cache, cos, sin, paired)
         # the position's cache row: normed latent, rotated shared key part
         if cache.write and cache.slots is not None:
             ops.latent_cache(self.dkv.forward(x), self.kv_norm.weight, self.kv_norm.eps, r, cache.pool, cache.slots,
@@ -102,7 +134,24 @@ class LatentAttention:
             values = torch.bmm(mixed.transpose(0, 1), self.uv.transpose(1, 2)).transpose(0, 1).reshape(tokens, H * V)
         return self.o.forward(values)
 
+    def _forward_per_head(self, x, ctx: StepContext, cache: CacheView, cos, sin, paired: bool) -> torch.Tensor:
+        tokens, H, D, R, V, r, hd = x.shape[0], self.heads, self.dim, self.rot, self.vdim, self.rank, self.head_size
+        # [normed latent | rotated shared key part] of this step's tokens, then every head's keys and values
+        rows = ops.latent_cache(self.dkv.forward(x), self.kv_norm.weight, self.kv_norm.eps, r, None, None,
+                                ctx.positions, cos, sin, paired)
+        widened = self.kv_up.forward(rows[:, :r])                                       # [tokens, H * D + H * V]
+        q = self.uq.forward(self.q_norm.forward(self.dq.forward(x), self.dtype))       # [tokens, H * (D + R)]
+        q_heads = torch.empty((tokens, H, hd), dtype=self.dtype, device=x.device)
+        write = cache.write and cache.slots is not None
+        ops.latent_heads(q, widened, rows, r, q_heads, cache.pool if write else None, cache.slots if write else None,
+                         ctx.positions, cos, sin, paired, D, R, V)
+        out, _ = attend_cached(q_heads, cache, ctx, scale=self.scale, split_decode=self.split_decode, flash=self.flash)
+        return self.o.forward(out.view(tokens, H * hd))
+
     def weight_bytes(self) -> int:
+        if self.per_head:
+            return (self.dq.weight_bytes() + self.uq.weight_bytes() + self.dkv.weight_bytes() + self.o.weight_bytes()
+                    + self.kv_up.weight_bytes())
         element = self.uk.element_size()
         return (self.dq.weight_bytes() + self.uq.weight_bytes() + self.dkv.weight_bytes() + self.o.weight_bytes()
                 + (self.uk.numel() + self.uv.numel()) * element)
