@@ -981,10 +981,11 @@ def design_zitezen(args):
         gate = torch.randn(tokens, H * V, device="cuda")
         wide = torch.ones(H * V, device="cuda")
         gate_up = torch.randn(tokens, 2 * H * V, device="cuda").to(bf16)
+        up_only = torch.randn(tokens, H * V, device="cuda").to(bf16)
         kernels[f"after_the_heads_{tokens}"] = {
             "zitezen: per-head unit RMS, weight, sigmoid gate": gbs(
                 tokens * H * V * (4 + 4 + 2), lambda: ops.head_norm_gate(heads_out, wide, gate, H, 1e-5, bf16)),
-            "zitezen: relu(u)^2": gbs(tokens * H * V * 2 * 2, lambda: ops.relu_squared(gate_up[:, :H * V].contiguous())),
+            "zitezen: relu(u)^2": gbs(tokens * H * V * 2 * 2, lambda: ops.relu_squared(up_only)),
             "qwen3: silu(gate) * up": gbs(tokens * H * V * 2 * 3, lambda: ops.silu_mul(gate_up))}
     # one decode step of 8 requests: the recurrence's state against attention's cached keys and values
     batch, context = 8, prompt
@@ -1026,7 +1027,10 @@ def design_zitezen(args):
     state.zero_()
     one_row, length = ints([0]), ints([tokens])
     kernels[f"prompt_mixer_{tokens}"] = {
-        "zitezen: recurrence, token by token": tflops(
+        "zitezen: recurrence, in chunks of 16 tokens": tflops(
+            tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, one_row, length,
+                                                             one_row, H, D, V, longest=tokens)),
+        "zitezen: recurrence, token by token (the form of decode steps)": tflops(
             tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, one_row, length,
                                                              one_row, H, D, V))}
     pages = -(-tokens // 16)

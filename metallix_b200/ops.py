@@ -41,7 +41,7 @@ _SIGNATURES = {
     "mxb_weighted_sum": [_P, _P, _P, _L, _L, _F, _F, _I, _I, _I, _P],
     "mxb_mlstm_state_values": [_I, _I, _I],
     "mxb_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _L, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
-                       _P, _P],
+                       _I, _P, _P],
     "mxb_head_norm_gate": [_P, _P, _P, _L, _I, _P, _I, _I, _I, _I, _F, _P],
     "mxb_latent_cache": [_P, _L, _P, _F, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "mxb_latent_heads": [_P, _L, _P, _L, _P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
@@ -462,7 +462,7 @@ def mlstm_state_values(heads: int, dim: int, vdim: int) -> int:
 
 def mlstm_scan(proj: torch.Tensor, offsets, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float,
                state: torch.Tensor, row_start: torch.Tensor, row_length: torch.Tensor,
-               request_slots: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
+               request_slots: torch.Tensor, heads: int, dim: int, vdim: int, longest: int = 1) -> torch.Tensor:
     """The matrix-memory recurrence over a step's tokens. ``proj``
     ``[tokens, columns]`` holds, from the column ``offsets`` (q, k, v, i, f)
     on, heads * dim queries and keys, heads * vdim values and one input- and
@@ -471,7 +471,10 @@ def mlstm_scan(proj: torch.Tensor, offsets, i_bias: torch.Tensor, f_bias: torch.
     (0: a padding row) and owns slot ``request_slots[r]`` of ``state``
     (float32 ``[slots, mlstm_state_values]``, advanced in place). Returns
     float32 ``[tokens, heads * vdim]``: each head's C^T q over its bounded
-    normaliser, before the head norm."""
+    normaliser, before the head norm. ``longest`` (the most tokens any row
+    brings, as the host knows it) chooses the form: from 8 tokens on the
+    rows are worked on in chunks of 16 tokens side by side, below that token
+    by token; the two agree to rounding."""
     _need(proj.is_cuda and proj.dtype in _CODES and proj.dim() == 2 and proj.stride(1) == 1,
           "proj must be a CUDA [tokens, columns] tensor with unit column stride")
     _check(state, "state", (torch.float32,), 2)
@@ -492,7 +495,7 @@ def mlstm_scan(proj: torch.Tensor, offsets, i_bias: torch.Tensor, f_bias: torch.
     _call("mxb_mlstm_scan", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, i_off, f_off, i_bias.data_ptr(),
           f_bias.data_ptr(), float(cap), float(dim) ** -0.5, state.data_ptr(), state.stride(0), state.shape[0],
           row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(), out.data_ptr(), rows, heads, dim,
-          vdim, _CODES[proj.dtype], status_word(proj.device).data_ptr(), _stream())
+          vdim, _CODES[proj.dtype], int(longest), status_word(proj.device).data_ptr(), _stream())
     return out
 
 

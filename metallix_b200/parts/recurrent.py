@@ -37,12 +37,16 @@ from .registry import CacheView, Prepared, Runtime, StepContext, StepPlan, Weigh
 
 def request_rows(plan: StepPlan) -> Prepared:
     """Where each request row's tokens lie in the packed step: ``row_start``
-    and ``row_length`` (0 for a padding row, which owns no state)."""
+    and ``row_length`` (0 for a padding row, which owns no state); ``longest``,
+    the most tokens any row brings, decides which form of the recurrence's
+    kernel runs (and with it which steps may share a captured graph)."""
     counts = np.asarray(plan.counts, dtype=np.int64)
     starts = np.zeros(len(counts), dtype=np.int64)
     np.cumsum(counts[:-1], out=starts[1:])
     lengths = np.where(np.arange(len(counts)) < plan.live, counts, 0)
-    return Prepared({"row_start": starts.astype(np.int32), "row_length": lengths.astype(np.int32)}, {}, graph_key=None)
+    longest = int(counts.max()) if len(counts) else 1
+    return Prepared({"row_start": starts.astype(np.int32), "row_length": lengths.astype(np.int32)},
+                    {"longest": longest}, graph_key=longest >= 8)
 
 
 class MatrixMemory:
@@ -94,7 +98,8 @@ class MatrixMemory:
                 raise ValueError("the recurrence's request rows were not prepared for this step")
             counts = [ctx.request_offsets[row + 1] - ctx.request_offsets[row] for row in range(ctx.num_requests)]
             prepared = request_rows(StepPlan(counts, ctx.request_positions, len(counts), 0))
-            rows = {name: torch.from_numpy(array).to(ctx.device) for name, array in prepared.arrays.items()}
+            rows = dict(prepared.facts)
+            rows.update({name: torch.from_numpy(array).to(ctx.device) for name, array in prepared.arrays.items()})
             ctx.extras[self.step_key] = rows
         return rows
 
@@ -107,7 +112,7 @@ class MatrixMemory:
         memory = ops.mlstm_scan(proj, (at["q_proj"], at["k_proj"], at["v_proj"], at["input_gate_proj"],
                                        at["forget_gate_proj"]), self.input_bias, self.forget_bias, self.cap,
                                 cache.state, rows["row_start"], rows["row_length"], ctx.request_slots,
-                                self.heads, self.dim, self.vdim)
+                                self.heads, self.dim, self.vdim, longest=rows.get("longest", 1))
         gate = proj[:, at["gate_proj"]:at["gate_proj"] + self.heads * self.vdim]
         return self.o.forward(ops.head_norm_gate(memory, self.norm_weight, gate, self.heads, self.eps, self.dtype))
 

@@ -346,14 +346,19 @@ def test_tanh_norm_as_a_norm_part_and_small_sums():
 @gpu
 @pytest.mark.parametrize("heads, dim, vdim", [(3, 8, 20), (1, 16, 33), (2, 64, 64), (4, 5, 4), (2, 130, 96)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_matrix_memory_kernel(heads, dim, vdim, dtype):
+@pytest.mark.parametrize("form", ["token by token", "in chunks"])
+def test_matrix_memory_kernel(heads, dim, vdim, dtype, form):
     """The recurrence over three requests of unequal length in one launch (one
     of them a single token, one a padding row), then continued in a second
     launch from the state the first left, against the plain recurrence run in
-    one piece; a slot is zeroed and used again."""
+    one piece; a slot is zeroed and used again. Both forms of the kernel: token
+    by token, and in chunks of 16 tokens (a whole chunk and a rest, a single
+    token, less than a chunk; the second launch starts from a state that is
+    not zero)."""
     from metallix_b200 import ops
     rng = np.random.default_rng(heads * dim + vdim)
     cap, lengths = 7.0, [19, 1, 0, 11]
+    longest = max(lengths) if form == "in chunks" else 1
     k_size, v_size = heads * dim, heads * vdim
     columns = 2 * k_size + 2 * v_size + 2 * heads + 5
     at = {"q": 2, "k": 2 + k_size, "v": 2 + 2 * k_size, "g": 2 + 2 * k_size + v_size, "i": 2 + 2 * k_size + 2 * v_size}
@@ -378,7 +383,7 @@ def test_matrix_memory_kernel(heads, dim, vdim, dtype):
             cursor += length
         got = ops.mlstm_scan(device_proj, (at["q"], at["k"], at["v"], at["i"], at["f"]), dev(i_bias), dev(f_bias), cap,
                              state, dev(starts, torch.int32), dev(lengths, torch.int32), dev(slots, torch.int32),
-                             heads, dim, vdim)
+                             heads, dim, vdim, longest=longest)
         ops.check_status("cuda")
         for row, (start, length) in enumerate(zip(starts, lengths)):
             outs.setdefault(row, []).append(got[start:start + length].double().cpu().numpy())
