@@ -955,7 +955,7 @@ def design_zitezen(args):
 
     ops.require_cuda()
     kernels = {}
-    size = "8b-layers" if not args.kernels_only else "0.6b-layers"
+    size = "8b-layers"
     hidden, heads, kv_heads, dim, inter = DESIGN_SIZES[size]
     memory, latent, _ = ZITEZEN_SIZES[size]
     bf16, f32 = torch.bfloat16, torch.float32

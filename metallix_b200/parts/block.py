@@ -116,10 +116,15 @@ class StreamWrite:
     channel_scale: Optional[torch.Tensor]   # [hidden] or None
     mix: torch.Tensor                       # [s, s], indexed [from, to]
     out_weights: torch.Tensor               # [s]
+    second: Optional[torch.Tensor] = None   # a second result: weights[0] * result + weights[1] * second is what joins
+    weights: tuple = (1.0, 1.0)
+
+    def fields(self) -> dict:
+        return dict(result=self.result, channel_scale=self.channel_scale, mix=self.mix, out_weights=self.out_weights,
+                    second=self.second, weights=self.weights)
 
     def settle(self, streams: torch.Tensor) -> None:
-        ops.stream_mix(streams, result=self.result, channel_scale=self.channel_scale, mix=self.mix,
-                       out_weights=self.out_weights, read=False)
+        ops.stream_mix(streams, read=False, **self.fields())
 
 
 def read_streams(streams: torch.Tensor, pending, in_weights: Optional[torch.Tensor], norm, out_dtype: torch.dtype,
@@ -130,8 +135,7 @@ def read_streams(streams: torch.Tensor, pending, in_weights: Optional[torch.Tens
     if pending is not None and not isinstance(pending, StreamWrite):
         settle(streams, pending)
         pending = None
-    write = dict(result=pending.result, channel_scale=pending.channel_scale, mix=pending.mix,
-                 out_weights=pending.out_weights) if pending is not None else {}
+    write = pending.fields() if pending is not None else {}
     if getattr(norm, "elementwise", False) and getattr(norm, "kind", None) == "dynamic_tanh":
         return ops.stream_mix(streams, in_weights=in_weights, alpha=norm.alpha, norm_weight=norm.weight,
                               norm_bias=norm.bias, out_dtype=out_dtype, rows_index=rows_index,
@@ -169,6 +173,9 @@ class HyperConnectionBlock:
                 raise ValueError(f"{layer.name}: a feed-forward needs its norm")
             self.feed_forward_norm = build_part("norm", layer.feed_forward_norm, weights, runtime)
         self.dtype = runtime.dtype
+        # A mixer made of two may hand both results over with their weights: the sum is then made by the kernel
+        # that writes the streams, not by one of its own.
+        self.mix_pair = getattr(self.mixer, "forward_pair", None)
         s = self.streams
 
         def small(name, shape):
@@ -195,7 +202,11 @@ class HyperConnectionBlock:
         ``pending`` still to join; returns the last sublayer's ``StreamWrite``."""
         own = self.mixer_streams
         mixer_in = read_streams(streams, pending, own["in"], self.mixer_norm, self.dtype)
-        left = StreamWrite(self.mixer.forward(mixer_in, ctx, cache), own["scale"], own["mix"], own["out"])
+        if self.mix_pair is not None:
+            first, second, weights = self.mix_pair(mixer_in, ctx, cache)
+            left = StreamWrite(first, own["scale"], own["mix"], own["out"], second=second, weights=weights)
+        else:
+            left = StreamWrite(self.mixer.forward(mixer_in, ctx, cache), own["scale"], own["mix"], own["out"])
         if self.feed_forward is None:
             return left
         own = self.feed_forward_streams

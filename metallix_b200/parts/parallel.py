@@ -25,12 +25,18 @@ class ParallelMixers:
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kind="several", members=(self.left.cache_need(), self.right.cache_need()))
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+    def forward_pair(self, x: torch.Tensor, ctx: StepContext, cache: CacheView):
+        """(left result, right result, (left_scale, right_scale)) for a caller
+        that adds them up itself in a pass it makes anyway."""
         if len(cache.members) != 2:
             raise ValueError("two mixers side by side need a cache view with two members")
         left = self.left.forward(x, ctx, cache.members[0])
         right = self.right.forward(x, ctx, cache.members[1])
-        return ops.weighted_sum(left, right, self.left_scale, self.right_scale)
+        return left, right, (self.left_scale, self.right_scale)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        left, right, (a, b) = self.forward_pair(x, ctx, cache)
+        return ops.weighted_sum(left, right, a, b)
 
     def weight_bytes(self) -> int:
         return self.left.weight_bytes() + self.right.weight_bytes()
