@@ -893,7 +893,7 @@ ZITEZEN_SIZES = {"0.6b-layers": ((8, 64, 128), (16, 64, 32, 64, 256, 384), (4, 6
 
 def _zitezen(hidden, heads, kv_heads, dim, inter, size):
     memory, latent, beside = ZITEZEN_SIZES[size]
-    recurrence = lambda m: {"heads": m[0], "dim": m[1], "vdim": m[2], "gate_cap": 15.0}
+    recurrence = lambda m: {"heads": m[0], "dim": m[1], "vdim": m[2], "gate_cap": 10.0}
     rot = lambda dims: {"base": 1.0e4, "dims": dims}
     through_latent = {"heads": latent[0], "dim": latent[1], "rot_dim": latent[2], "vdim": latent[3],
                       "kv_rank": latent[4], "q_rank": latent[5], "scale": (latent[1] + latent[2]) ** -0.5,
@@ -903,10 +903,10 @@ def _zitezen(hidden, heads, kv_heads, dim, inter, size):
     mlp = {"kind": "dense", "ff": inter}
     four = [{"type": "mlstm", "mixer": recurrence(memory), "mlp": None},
             {"type": "latent_attention", "mixer": through_latent, "mlp": mlp},
-            {"type": "parallel", "mixer": {"left": grouped, "right": recurrence(beside), "left_scale": 0.6,
-                                           "right_scale": 0.9}, "mlp": mlp},
+            {"type": "parallel", "mixer": {"left": grouped, "right": recurrence(beside), "left_scale": 0.5,
+                                           "right_scale": 0.5}, "mlp": mlp},
             {"type": "mlstm", "mixer": recurrence(memory), "mlp": None}]
-    return {"architecture": "Zitezen", "vocab": DESIGN_VOCAB, "width": hidden, "streams": 2, "norm": {"eps": 1e-5},
+    return {"architecture": "Zitezen", "vocab": DESIGN_VOCAB, "width": hidden, "streams": 2, "norm": {"eps": 1e-6},
             "layers": four * (DESIGN_LAYERS // 4)}
 
 
@@ -998,7 +998,7 @@ def design_zitezen(args):
     rows, ones_int = ints(list(range(batch))), ints([1] * batch)
     kernels["decode_step_mixer_8_requests"] = {
         "zitezen: recurrence, state read and written": gbs(
-            2 * state.numel() * 4, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, rows, ones_int, rows,
+            2 * state.numel() * 4, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, state, rows, ones_int, rows,
                                                           H, D, V))}
     pages = batch * (-(-context // 16))
     table = torch.arange(pages, dtype=torch.int32, device="cuda").view(batch, -1)
@@ -1028,10 +1028,10 @@ def design_zitezen(args):
     one_row, length = ints([0]), ints([tokens])
     kernels[f"prompt_mixer_{tokens}"] = {
         "zitezen: recurrence, in chunks of 16 tokens": tflops(
-            tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, one_row, length,
+            tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, state, one_row, length,
                                                              one_row, H, D, V, longest=tokens)),
         "zitezen: recurrence, token by token (the form of decode steps)": tflops(
-            tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 15.0, state, one_row, length,
+            tokens * H * 4.0 * D * V, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, state, one_row, length,
                                                              one_row, H, D, V))}
     pages = -(-tokens // 16)
     table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, -1)

@@ -276,7 +276,7 @@ def rounded(array, dtype):
 
 
 @gpu
-@pytest.mark.parametrize("streams, width, rows", [(1, 72, 5), (2, 256, 9), (3, 331, 4), (8, 64, 3)])
+@pytest.mark.parametrize("streams, width, rows", [(1, 72, 5), (2, 192, 9), (3, 331, 4), (4, 100, 6), (8, 64, 3)])
 @pytest.mark.parametrize("result_dtype", [torch.float32, torch.bfloat16])
 def test_streams_write_read_and_tanh_norm(streams, width, rows, result_dtype):
     """One kernel: a result joins all streams through the mixing matrix, the
@@ -344,7 +344,7 @@ def test_tanh_norm_as_a_norm_part_and_small_sums():
 
 
 @gpu
-@pytest.mark.parametrize("heads, dim, vdim", [(3, 8, 20), (1, 16, 33), (2, 64, 64), (4, 5, 4), (2, 130, 96)])
+@pytest.mark.parametrize("heads, dim, vdim", [(3, 8, 20), (1, 16, 33), (2, 64, 64), (4, 5, 4), (2, 130, 96), (1, 264, 40)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("form", ["token by token", "in chunks"])
 def test_matrix_memory_kernel(heads, dim, vdim, dtype, form):
