@@ -313,6 +313,16 @@ def test_streams_write_read_and_tanh_norm(streams, width, rows, result_dtype):
     # the write alone
     ops.stream_mix(held, result=wide[:, 3:3 + width], channel_scale=dev(scale), mix=dev(mixing), out_weights=dev(out_w), read=False)
     assert np.abs(held.double().cpu().numpy().transpose(1, 0, 2) - new).max() < 2e-5
+    # two results with weights (two mixers side by side): 0.7 y - 0.4 z joins
+    z = rounded(rng.normal(size=(rows, width)) * 3.0, result_dtype)
+    held = dev(x.transpose(1, 0, 2)).contiguous()
+    got = ops.stream_mix(held, result=wide[:, 3:3 + width], second=dev(z, result_dtype), weights=(0.7, -0.4),
+                         channel_scale=dev(scale), mix=dev(mixing), out_weights=dev(out_w), in_weights=dev(in_w),
+                         out_dtype=torch.float32)
+    both = plain.write_streams(f32(x), f32(mixing), f32(out_w),
+                               (float(np.float32(0.7)) * y + float(np.float32(-0.4)) * z) * f32(scale))
+    assert np.abs(held.double().cpu().numpy().transpose(1, 0, 2) - both).max() < 3e-5
+    assert np.abs(got.double().cpu().numpy() - plain.read_streams(both, f32(in_w))).max() < 1e-4
 
 
 @gpu
@@ -449,6 +459,50 @@ def test_latent_rows_into_the_cache_and_rotated_query_parts(dtype, rank, rot, he
     want = plain.turn(q.reshape(tokens, heads, dim + rot)[:, :, dim:], positions, base, rot, neighbours=True)
     got = target.double().cpu().numpy()
     assert np.abs(got[:, :, rank:] - want).max() < tolerance and (got[:, :, :rank] == 0.0).all()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, dim, rot, vdim, size", [(4, 12, 6, 10, 64), (2, 32, 16, 64, 64), (3, 40, 24, 70, 128)])
+def test_rows_per_head_from_a_widened_latent(dtype, heads, dim, rot, vdim, size):
+    """Queries [q_u | rot(q_r) | 0], keys [k_h | shared rotated part | 0] and
+    values [v_h | 0] per head, padded to the head size, the rows at their slots
+    of a two-plane pool; a token without a slot writes its query only."""
+    from metallix_b200 import ops
+    rng = np.random.default_rng(heads * dim + vdim)
+    tokens, page, pages, base = 19, 4, 7, 100.0
+    positions = rng.permutation(40)[:tokens]
+    slots = rng.permutation(page * pages)[:tokens]
+    slots[2] = -1
+    q = rounded(rng.normal(size=(tokens, heads * (dim + rot))), dtype)
+    up = rounded(rng.normal(size=(tokens, heads * (dim + vdim))), dtype)
+    shared = rounded(rng.normal(size=(tokens, 5 + rot)), dtype)       # the rotated part lies from column 5 on
+    frequency = base ** (-2.0 * np.arange(rot // 2) / rot)
+    angle = torch.arange(48, dtype=torch.float64)[:, None] * torch.tensor(frequency)[None, :]
+    cos, sin = torch.cos(angle).float().cuda().contiguous(), torch.sin(angle).float().cuda().contiguous()
+    q_heads = torch.full((tokens, heads, size), 7.0, dtype=dtype, device="cuda")
+    pool = torch.full((pages, 2, heads, page, size), 7.0, dtype=dtype, device="cuda")
+    ops.latent_heads(dev(q, dtype), dev(up, dtype), dev(shared, dtype), 5, q_heads, pool, dev(slots, torch.int32),
+                     dev(positions, torch.int32), cos, sin, True, dim, rot, vdim)
+    ops.check_status("cuda")
+    per_head = q.reshape(tokens, heads, dim + rot)
+    want_q = np.zeros((tokens, heads, size))
+    want_q[:, :, :dim] = per_head[:, :, :dim]
+    want_q[:, :, dim:dim + rot] = plain.turn(per_head[:, :, dim:], positions, base, rot, neighbours=True)
+    tolerance = 1e-5 if dtype == torch.float32 else 3e-2
+    assert np.abs(q_heads.double().cpu().numpy() - want_q).max() < tolerance
+    got = pool.double().cpu().numpy()
+    written = np.zeros((pages, page), dtype=bool)
+    for t, slot in enumerate(slots):
+        if slot < 0:
+            continue
+        written[slot // page, slot % page] = True
+        keys, values = got[slot // page, 0, :, slot % page], got[slot // page, 1, :, slot % page]
+        assert np.array_equal(keys[:, :dim], up[t, :heads * dim].reshape(heads, dim))
+        assert np.array_equal(keys[:, dim:dim + rot], np.repeat(shared[t, None, 5:], heads, axis=0))
+        assert np.array_equal(values[:, :vdim], up[t, heads * dim:].reshape(heads, vdim))
+        assert (keys[:, dim + rot:] == 0.0).all() and (values[:, vdim:] == 0.0).all()
+    assert (got.transpose(0, 3, 1, 2, 4)[~written] == 7.0).all()
 
 
 @gpu
