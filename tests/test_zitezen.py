@@ -75,7 +75,16 @@ BARE = {"architecture": "Zitezen", "vocab": 97, "width": 48, "streams": 2, "norm
                                      memory(1, 16, 33, 6.0), -0.5, 1.0), 64),
             layer("parallel", beside(grouped(2, 2, 8, 8, 0.4, 2.0, None), memory(3, 4, 4, 9.0), 1.0, 1.0), 0),
             layer("latent_attention", latent(3, 8, 4, 6, 12, 10, 0.35, 30.0), 40)]}
-MODELS = {"small": (SMALL, 21, 8, 1.0), "wide": (WIDE, 22, 16, 1.0), "bare": (BARE, 23, 4, 1.0),
+# TALL: heads of 128 with four query heads per key/value head (the tensor-core prompt kernels and the
+# split-key decode kernel at that size, with capped scores), a latent attention whose rows per head are 128
+# wide (96 + 32) and one whose rows are 256 wide (values of 200), a recurrence with keys of 96.
+TALL = {"architecture": "Zitezen", "vocab": 150, "width": 96, "streams": 2, "norm": {"eps": 1e-5},
+        "layers": [
+            layer("parallel", beside(grouped(4, 1, 128, 128, 0.09, 8.0, {"base": 1.0e4, "dims": 64}),
+                                     memory(2, 96, 48, 11.0), 0.8, 0.7), 0),
+            layer("latent_attention", latent(2, 96, 32, 80, 40, 24, 0.1, 1.0e3), 64),
+            layer("latent_attention", latent(2, 150, 10, 200, 32, 16, 0.08, 1.0e2), 0)]}
+MODELS = {"small": (SMALL, 21, 8, 1.0), "wide": (WIDE, 22, 16, 1.0), "bare": (BARE, 23, 4, 1.0), "tall": (TALL, 25, 16, 1.0),
           # query/key norm weights three times as large: scores nine times as far apart, so that which keys a
           # query sees decides its output (float32 only, a bound of its own)
           "sharp": (SMALL, 24, 8, 3.0)}
@@ -158,7 +167,7 @@ def make_engine(folders, name, dtype, pages=96, latent_cache=None, **options):
 # ------------------------------------------------ configuration (no GPU needed)
 def test_configuration_round_trip_and_registry():
     from metallix_b200.config import ConfigError, ZitezenConfig, parse_config, resolve
-    for raw in (SMALL, WIDE, BARE):
+    for raw in (SMALL, WIDE, BARE, TALL):
         config = parse_config(raw)
         assert isinstance(config, ZitezenConfig) and resolve(raw).kind == "zitezen"
         assert ZitezenConfig.from_dict(config.to_dict()) == config
@@ -564,6 +573,75 @@ def test_general_attention_kernel_one_key_that_stands_out(dtype, planes, heads, 
     want *= plain.sigmoid(gate)[:, :, None] if per_head else plain.sigmoid(gate).reshape(tail, heads, vdim)
     assert weight_on_far > 5.0 / context      # the far key weighs many times its share in the last output, capped or not
     assert np.abs(out.double().cpu().numpy() - want).max() < (2e-5 if dtype == torch.float32 else 3e-2)
+
+
+@gpu
+@pytest.mark.parametrize("dtype, head_dim, heads, kv_heads, context, page", [
+    (torch.bfloat16, 64, 6, 6, 300, 16), (torch.bfloat16, 128, 16, 8, 4500, 16), (torch.bfloat16, 128, 8, 2, 700, 4),
+    (torch.bfloat16, 256, 4, 4, 400, 16), (torch.float32, 64, 4, 2, 500, 8), (torch.float32, 128, 2, 1, 260, 16)])
+def test_capped_scores_in_the_split_key_and_prompt_kernels(dtype, head_dim, heads, kv_heads, context, page):
+    """c tanh(s / c) ahead of the softmax inside the split-key decode kernels
+    (four single tokens behind contexts of unequal length: short ones, and
+    long ones that a block walks over tile by tile) and inside both
+    tensor-core prompt kernels (a portion behind cached keys), with a gate,
+    against numpy. The cap is low enough to bend most scores."""
+    from metallix_b200 import ops
+    rng = np.random.default_rng(head_dim + context)
+    cap, scale, rows = 1.5, 0.3, 4
+    lengths = [context, context // 2 + 3, 1, context - 7]
+    pages_each = -(-context // page)
+    pool_pages = rows * pages_each + 2
+    keys = rounded(rng.normal(size=(rows, context, kv_heads, head_dim)), dtype)
+    values = rounded(rng.normal(size=(rows, context, kv_heads, head_dim)), dtype)
+    order = rng.permutation(pool_pages)[:rows * pages_each].reshape(rows, pages_each)
+    pool = torch.zeros((pool_pages, 2, kv_heads, page, head_dim), dtype=dtype, device="cuda")
+    for r in range(rows):
+        k_pages = np.zeros((pages_each * page, kv_heads, head_dim))
+        v_pages = np.zeros_like(k_pages)
+        k_pages[:context], v_pages[:context] = keys[r], values[r]
+        index = torch.tensor(order[r], device="cuda")
+        pool[index, 0] = dev(k_pages.reshape(pages_each, page, kv_heads, head_dim).transpose(0, 2, 1, 3), dtype)
+        pool[index, 1] = dev(v_pages.reshape(pages_each, page, kv_heads, head_dim).transpose(0, 2, 1, 3), dtype)
+    group = heads // kv_heads
+
+    def attend(q, row, last):      # q [heads, head_dim] at position `last` of request `row`
+        k = np.repeat(keys[row, :last + 1], group, axis=1)
+        v = np.repeat(values[row, :last + 1], group, axis=1)
+        scores = cap * np.tanh(np.einsum("hd,jhd->hj", q, k) * scale / cap)
+        weights = np.exp(scores - scores.max(axis=1, keepdims=True))
+        weights /= weights.sum(axis=1, keepdims=True)
+        return np.einsum("hj,jhd->hd", weights, v)
+
+    tolerance = 2e-5 if dtype == torch.float32 else 3e-2
+    q = rounded(rng.normal(size=(rows, heads, head_dim)), dtype)
+    gate = rounded(rng.normal(size=(rows, heads * head_dim)), dtype)
+    out = torch.empty((rows, heads, head_dim), dtype=dtype, device="cuda")
+    positions = [length - 1 for length in lengths]
+    if ops.decode_attention_supported(head_dim, heads, kv_heads, dtype):
+        ops.paged_attention_decode(dev(q, dtype), pool, out, dev(order, torch.int32), dev(range(rows), torch.int32),
+                                   dev(range(rows), torch.int32), dev(positions, torch.int32), scale, max(lengths),
+                                   gate=dev(gate, dtype), softcap=cap)
+        ops.check_status("cuda")
+        want = np.stack([attend(q[r], r, positions[r]) for r in range(rows)]) * plain.sigmoid(gate).reshape(rows, heads, head_dim)
+        assert np.abs(out.double().cpu().numpy() - want).max() < tolerance
+    if ops.flash_prefill_supported(head_dim, heads, kv_heads, dtype):
+        cached, portion = min(100, context // 3), min(150, context - context // 3)
+        q = rounded(rng.normal(size=(portion, heads, head_dim)), dtype)
+        gate = rounded(rng.normal(size=(portion, heads * head_dim)), dtype)
+        out = torch.empty((portion, heads, head_dim), dtype=dtype, device="cuda")
+        tile = ops.flash_prefill_tile()
+        starts = list(range(0, portion, tile))
+        want = np.stack([attend(q[t], 0, cached + t) for t in range(portion)]) * plain.sigmoid(gate).reshape(portion, heads, head_dim)
+        for kernel in ("tcgen05", "mma"):
+            if kernel == "tcgen05" and not ops.flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page, dtype):
+                continue
+            out.zero_()
+            ops.flash_prefill(dev(q, dtype), pool, out, dev(order[:1], torch.int32), dev([0] * len(starts), torch.int32),
+                              dev(starts, torch.int32), dev([min(tile, portion - s) for s in starts], torch.int32),
+                              dev(range(cached, cached + portion), torch.int32), scale, kernel=kernel,
+                              longest_context=cached + portion, gate=dev(gate, dtype), softcap=cap)
+            ops.check_status("cuda")
+            assert np.abs(out.double().cpu().numpy() - want).max() < tolerance, kernel
 
 
 # ------------------------------------------------- the engine: whole prompts
