@@ -147,6 +147,7 @@ namespace mxb {
 // out = max(x, 0)^2: the activation of a feed-forward without a gate, float32 inside.
 template <typename T>
 __global__ void relu_squared_kernel(T* __restrict__ out, const T* __restrict__ x, size_t count) {
+  chain_release();
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const float v = fmaxf(to_float(x[i]), 0.0f);
@@ -159,6 +160,7 @@ namespace mxb {
 // Eight bfloat16 values per thread (16-byte loads and stores).
 __global__ void relu_squared_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                                            size_t groups) {
+  chain_release();
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < groups;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const uint4 raw = *reinterpret_cast<const uint4*>(x + i * 8);

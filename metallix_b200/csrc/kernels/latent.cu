@@ -38,6 +38,7 @@ __global__ void latent_cache_kernel(const T* __restrict__ x, long long ld, const
                                     int table_positions, const int* __restrict__ positions,
                                     const int* __restrict__ slots, T* __restrict__ cache, int page_tokens,
                                     int num_pages, int* status) {
+  chain_release();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int slot = slots != nullptr ? slots[t] : t;   // without slots: row t of a plain [tokens, rank + rot] buffer
@@ -69,6 +70,7 @@ __global__ void rotate_into_kernel(const T* __restrict__ src, long long ld_src, 
                                    int interleaved, const float* __restrict__ cos_table,
                                    const float* __restrict__ sin_table, int table_positions,
                                    const int* __restrict__ positions, int* status) {
+  chain_release();
   const int t = blockIdx.x;
   int pos = positions[t];
   if (pos < 0 || (rotary_dim > 0 && pos >= table_positions)) {
@@ -100,6 +102,7 @@ __global__ void latent_heads_kernel(const T* __restrict__ q, long long ld_q, con
                                     const float* __restrict__ sin_table, int table_positions, int rotary_dim,
                                     int interleaved, int heads, int D, int R, int V, int hd, int page_tokens,
                                     int num_pages, int* status) {
+  chain_release();
   const int t = blockIdx.x;
   int pos = positions[t];
   if (pos < 0 || (rotary_dim > 0 && pos >= table_positions)) {

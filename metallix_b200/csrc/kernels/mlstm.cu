@@ -42,6 +42,7 @@ mlstm_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off
                   const int* __restrict__ row_start, const int* __restrict__ row_length,
                   const int* __restrict__ request_slots, float* __restrict__ out, int heads, int dim, int vdim,
                   int* status) {
+  chain_release();   // the kernel behind may start and fetch its weights meanwhile
   extern __shared__ float shared[];
   float* sC = shared;                         // [dim][32]
   float* sn = sC + dim * kSliceColumns;       // [dim]
@@ -133,6 +134,7 @@ mlstm_scan_registers_kernel(const T* __restrict__ proj, long long ld, int q_off,
                             const int* __restrict__ row_start, const int* __restrict__ row_length,
                             const int* __restrict__ request_slots, float* __restrict__ out, int heads, int dim, int vdim,
                             int* status) {
+  chain_release();   // the kernel behind may start and fetch its weights meanwhile
   constexpr int kMaxDim = 4 * R;
   __shared__ float sq[2][kMaxDim], sk[2][kMaxDim], sn[kMaxDim];
   __shared__ float red[2][kScanParts * kSliceColumns], red_nq[2][kScanParts];
@@ -247,6 +249,7 @@ mlstm_chunk_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                    float* __restrict__ state, long long slot_stride, int num_slots, const int* __restrict__ row_start,
                    const int* __restrict__ row_length, const int* __restrict__ request_slots, float* __restrict__ out,
                    int heads, int dim, int vdim, int* status) {
+  chain_release();   // the kernel behind may start and fetch its weights meanwhile
   constexpr int THREADS = kSliceColumns * PARTS;
   extern __shared__ float shared[];
   const int pitch = dim + 1;                          // rows of q and k a bank apart
@@ -416,6 +419,7 @@ template <typename TGate, typename TOut>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, const TGate* __restrict__ gate,
                       long long ldg, TOut* __restrict__ y, int pairs, int heads, int vdim, float eps) {
+  chain_release();
   const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (pair >= pairs) return;
   const int t = pair / heads, h = pair - t * heads;

@@ -43,6 +43,7 @@ struct StreamMixArgs {
 
 template <typename TResult, typename TOut>
 __global__ void __launch_bounds__(kMixThreads) stream_mix_kernel(StreamMixArgs a) {
+  chain_release();   // the kernel behind may start and fetch what no kernel writes (its weights) meanwhile
   __shared__ float s_mix[kMaxStreams * kMaxStreams], s_out[kMaxStreams], s_in[kMaxStreams];
   const int s = a.count;
   if (threadIdx.x < s * s) s_mix[threadIdx.x] = a.mix != nullptr ? a.mix[threadIdx.x] : 0.0f;
@@ -114,6 +115,7 @@ __device__ __forceinline__ void write4(__nv_bfloat16* p, float4 v) {
 // SM bounds the number of streams (1, 2, 4 or 8), so that a model with few of them holds few registers.
 template <typename TResult, typename TOut, int SM>
 __global__ void __launch_bounds__(kMixThreads) stream_mix_by4_kernel(StreamMixArgs a) {
+  chain_release();   // the kernel behind may start and fetch what no kernel writes (its weights) meanwhile
   __shared__ float s_mix[kMaxStreams * kMaxStreams], s_out[kMaxStreams], s_in[kMaxStreams];
   const int s = a.count;
   if (threadIdx.x < s * s) s_mix[threadIdx.x] = a.mix != nullptr ? a.mix[threadIdx.x] : 0.0f;
@@ -193,6 +195,7 @@ template <typename T>
 __global__ void __launch_bounds__(kMixThreads) weighted_sum_kernel(float* __restrict__ out, const T* __restrict__ x,
                                                                    const T* __restrict__ y, long long ldx, long long ldy,
                                                                    float a, float b, int rows, int width) {
+  chain_release();
   const long long total = static_cast<long long>(rows) * width;
   for (long long i = static_cast<long long>(blockIdx.x) * kMixThreads + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * kMixThreads) {
